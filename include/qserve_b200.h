@@ -297,15 +297,21 @@ QS_API int qs_hyb_retention(void* out, int64_t out_stride, float* prep, float* o
                             const float* inv_freq, int rot_dims, float k_scale, int gated, float* state, const int32_t* tok_pos,
                             const int32_t* entry_start, const int32_t* entry_len, const int32_t* entry_slot, const int32_t* entry_pos0,
                             int tokens_n, int entries, int heads, int dim, int vdim, float eps, int dtype, void* stream);
-/* Mixture-of-experts router: fp32 logits w_router [experts, width] h, softmax over all experts, the `top` largest scores kept as they are.
- * route fp32 [tokens, experts] (score of a chosen expert, 0 elsewhere), top_idx int32 / top_w fp32 [tokens, top], best first. */
+/* Mixture-of-experts router: fp32 logits z = w_router [experts, width] h.  route fp32 [tokens, experts] (weight of a chosen expert, 0
+ * elsewhere), top_idx int32 / top_w fp32 [tokens, top], best first (ties: the lower index).
+ * QS_ROUTER_SOFTMAX: scores softmax(z) over all experts, the `top` largest kept as they are (correction, groups, keep unused).
+ * QS_ROUTER_SIGMOID_GROUPS: scores s = sigmoid(z); the choice is made on s + correction (fp32 [experts], may be NULL): the experts form
+ * `groups` equal runs of neighbours, a group's score is the sum of its two largest choice scores, only experts of the `keep` best groups can
+ * be chosen, the `top` largest choice scores win; weights s / (sum of the winners' s + 1e-20). */
+#define QS_ROUTER_SOFTMAX 0
+#define QS_ROUTER_SIGMOID_GROUPS 1
 QS_API int qs_hyb_moe_router(float* route, int32_t* top_idx, float* top_w, const void* h, const float* w_router, int tokens_n, int width,
-                             int experts, int top, int dtype, void* stream);
+                             int experts, int top, int mode, const float* correction, int groups, int keep, int dtype, void* stream);
 /* Activation of all experts' columns of a token: in rows [F gate | F up], F = experts * ff + ff_shared (the shared expert's columns last);
- * g = min(gate, limit), u = clamp(up, -limit, limit), out = route[t, expert] g sigmoid(alpha g) (u + 1); shared columns: weight 1 and
- * limit_shared.  out [tokens, F]. */
+ * g = min(gate, limit), u = clamp(up, -limit, limit), out = route[t, expert] g sigmoid(alpha g) (u + shift); shared columns: weight 1 and
+ * limit_shared.  limit = +inf, alpha = 1, shift = 0 is silu(gate) * up.  out [tokens, F]. */
 QS_API int qs_hyb_moe_act(void* out, const void* in, const float* route, int tokens_n, int experts, int ff, float limit, int ff_shared,
-                          float limit_shared, float alpha, int dtype, void* stream);
+                          float limit_shared, float alpha, float shift, int dtype, void* stream);
 /* Expert-sorted rows of a mixture of experts.  Entry i = token * top + choice of top_idx [tokens, top]; the sorted order holds expert 0's
  * entries first, then expert 1's, ..., each in token order.  row_of [tokens * top]: the entry's sorted row; src_token [tokens * top]: the token of
  * a sorted row; ends [experts]: one past the last row of each expert.  work: int32, qs_hyb_moe_plan_work_ints(experts) elements. */
@@ -317,6 +323,50 @@ QS_API int qs_hyb_moe_gather(void* xs, const void* h, const int32_t* src_token, 
 /* y[t] = shared[t] + sum_k top_w[t, k] rows[row_of[t * top + k]]; y fp32 [tokens, width]; rows, shared (may be NULL) storage type */
 QS_API int qs_hyb_moe_combine(float* y, const void* rows, const void* shared, const int32_t* row_of, const float* top_w, int tokens_n, int top,
                               int width, int dtype, void* stream);
+
+/* Residual update and norm of a plain fp32 stream x [tokens, width]: x <- x + add1 + add2 + add_bias (each may be NULL; add1 / add2 rows fp32
+ * if their flag is set, else of the storage type; add_bias fp32 [width]); cat_out (may be NULL) <- [x | x0] per token in the storage type;
+ * out_h (may be NULL) <- norm of x: QS_NORM_RMS x rsqrt(mean x^2 + eps) w, QS_NORM_LAYER (x - mean) rsqrt(var + eps) w + b (b may be NULL). */
+#define QS_NORM_RMS 1
+#define QS_NORM_LAYER 2
+QS_API int qs_hyb_stream_update_norm(void* out_h, void* cat_out, float* x, const float* x0, const void* add1, int add1_f32, const void* add2,
+                                     int add2_f32, const float* add_bias, const float* w, const float* b, int kind, float eps, int tokens_n,
+                                     int width, int dtype, void* stream);
+/* out[t, i] = gelu_tanh(in[t, i] + bias[i]) (bias fp32, may be NULL); rows of in_stride / out_stride elements */
+QS_API int qs_hyb_bias_gelu_tanh(void* out, int64_t out_stride, const void* in, int64_t in_stride, const float* bias, int tokens_n, int ff,
+                                 int dtype, void* stream);
+/* x[i] <- cap tanh(x[i] / cap), fp32 in place */
+QS_API int qs_hyb_softcap(float* x, int64_t n, float cap, void* stream);
+
+/* Latent attention (csrc/hybrid_latent.cu): the pages hold, per position, kv_rank numbers of a normed latent and rot_dim numbers of a rotated
+ * key part shared by all heads: pool [page][page_size][kv_rank + rot_dim].
+ * qs_hyb_latent_prepare: from the rows of the first projection (query latent at column col_q, q_rank wide; key/value latent and rotated part
+ * at col_kv, kv_rank + rot_dim wide): cq [tokens, q_rank] = unit-RMS query latent times gain_q; the token's cell = [unit-RMS latent times
+ * gain_kv | rotated part].  Rotation: entry i < rot_dims/2 pairs with entry i + rot_dims/2, angle = position * inv_freq[i]. */
+QS_API int qs_hyb_latent_prepare(void* cq, const void* proj, int64_t stride, int col_q, int col_kv, const float* gain_q, const float* gain_kv,
+                                 const float* inv_freq, int rot_dims, const int32_t* tok_slot, const int32_t* tok_pos,
+                                 const int32_t* block_table, int max_blocks, void* pool, int tokens_n, int q_rank, int kv_rank, int rot_dim,
+                                 int page_size, float eps, int dtype, void* stream);
+/* qa [tokens, heads, kv_rank + rot_dim] = [qlat[head, token, :] | rotated q[token, head * (dim + rot_dim) + dim ...]]: the queries as they are
+ * scored against the cells (qlat [heads, tokens, kv_rank]: the unrotated query parts taken through the heads' key up-projections) */
+QS_API int qs_hyb_latent_query(void* qa, const void* qlat, const void* q, int64_t q_stride, const float* inv_freq, int rot_dims,
+                               const int32_t* tok_pos, int tokens_n, int heads, int dim, int kv_rank, int rot_dim, int dtype, void* stream);
+/* out [heads, tokens, kv_rank] = softmax-weighted sum of the cells' first kv_rank numbers over positions first..tok_pos (first as in
+ * qs_hyb_attention), scores scale * qa . cell in fp32.  Any shape with kv_rank <= 512. */
+QS_API int qs_hyb_latent_attention(void* out, const void* qa, const void* pool, const int32_t* tok_slot, const int32_t* tok_pos,
+                                   const int32_t* block_table, int max_blocks, int tokens_n, int heads, int kv_rank, int rot_dim, float scale,
+                                   int page_size, int chunk, int window, int dtype, void* stream);
+/* The same on the tensor cores (bfloat16 storage) where qs_hyb_latent_attention_fast_supported returns 1: the rows of a tile are (token, head)
+ * pairs of one entry.  scratch: fp32, qs_hyb_latent_attention_scratch_floats elements. */
+QS_API int qs_hyb_latent_attention_fast_supported(int dtype, int heads, int kv_rank, int rot_dim);
+QS_API int64_t qs_hyb_latent_attention_scratch_floats(int tokens, int heads, int kv_rank);
+QS_API int qs_hyb_latent_attention_fast(void* out, const void* qa, const void* pool, const int32_t* tok_slot, const int32_t* tok_pos,
+                                        const int32_t* block_table, int max_blocks, const int32_t* entry_start, const int32_t* entry_len,
+                                        const int32_t* entry_slot, const int32_t* entry_pos0, int entries, int tokens_n, float* scratch, int heads,
+                                        int kv_rank, int rot_dim, float scale, int page_size, int chunk, int window, int dtype, void* stream);
+/* out[t, h * vdim + j] = ov[h, t, j] * sigmoid(gate[t, col_g + h]) (gate may be NULL: no gate); ov [heads, tokens, vdim] */
+QS_API int qs_hyb_latent_gate_out(void* out, int64_t out_stride, const void* ov, const void* gate, int64_t gate_stride, int col_g, int tokens_n,
+                                  int heads, int vdim, int dtype, void* stream);
 
 #ifdef __cplusplus
 }

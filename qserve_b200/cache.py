@@ -15,8 +15,8 @@ from typing import Dict, List
 
 import torch
 
-from .modelcfg import (AttentionMixerConfig, DeltaMixerConfig, GateRecurrenceMixerConfig, HybridConfig, ParallelMixerConfig,
-                       RetentionMixerConfig)
+from .modelcfg import (AttentionMixerConfig, DeltaMixerConfig, GateRecurrenceMixerConfig, HybridConfig, LatentAttentionMixerConfig,
+                       ParallelMixerConfig, RetentionMixerConfig)
 
 
 class OutOfPages(RuntimeError):
@@ -69,12 +69,15 @@ class HybridCache:
         self.runs = [self.mixer_storage(cfg.layers[li].mixer) for li in cfg.schedule()]
 
     def mixer_storage(self, m) -> dict:
-        """What one run of a mixer keeps between steps: pages for an attention layer, a slot-indexed fp32 state for a recurrent one, both
-        (under "left" / "right") for two mixers side by side."""
+        """What one run of a mixer keeps between steps: pages for an attention layer (keys and values, or the latent rows of a latent
+        attention), a slot-indexed fp32 state for a recurrent one, both (under "left" / "right") for two mixers side by side."""
         dtype, device, page_size, max_seqs = self.dtype, self.device, self.page_size, self.max_seqs
         if isinstance(m, AttentionMixerConfig):
             return {"k": torch.zeros((self.num_pages, page_size, m.kv_heads, m.maps * m.dim), dtype=dtype, device=device),
                     "v": torch.zeros((self.num_pages, page_size, m.kv_heads, m.vdim), dtype=dtype, device=device)}
+        if isinstance(m, LatentAttentionMixerConfig):
+            # one row per position for all heads: the key/value latent and the rotated key part they share
+            return {"c": torch.zeros((self.num_pages, page_size, m.kv_rank + m.rot_dim), dtype=dtype, device=device)}
         if isinstance(m, DeltaMixerConfig):
             c = 2 * m.kv_heads * m.dim + m.heads * m.vdim
             return {"state": torch.zeros((max_seqs, m.heads, m.dim, m.vdim), dtype=torch.float32, device=device),

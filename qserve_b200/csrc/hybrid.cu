@@ -201,14 +201,6 @@ __global__ void rope_append_kernel(ST* __restrict__ proj, long long stride, cons
 // d, d + blockDim, ... for every map.  Epilogue:
 //   MAPS == 2: o = a1 - lambda a2;   then (head_norm) o <- o * rsqrt(mean(o^2) + eps);   o <- o * out_scale
 // ---------------------------------------------------------------------------------------------------------------------------------
-// first position a query at `pos` sees: the start of its chunk of `chunk` positions (0: no chunks), and not further back than `window`
-// positions including its own (0: no window)
-__host__ __device__ __forceinline__ int first_key(int pos, int chunk, int window) {
-  int f = chunk > 0 ? pos - pos % chunk : 0;
-  if (window > 0) f = max(f, pos - window + 1);
-  return f;
-}
-
 constexpr int kAttnThreads = 128;
 constexpr int kAttnKT = 128;
 constexpr int kAttnMaxV = 4;  // value dims per thread: Dv <= 512

@@ -288,9 +288,85 @@ __global__ void qk_prepare_append_kernel(ST* __restrict__ proj, long long stride
 // ---------------------------------------------------------------------------------------------------------------------------------
 constexpr int kRouterEPW = 4;
 
+// Grouped sigmoid routing of one token by one warp.  zk [3 E]: logits in, then choice scores | scores | group scores.
+//   s_e = sigmoid(z_e); choice c_e = s_e + correction_e; experts form `groups` equal runs of neighbours, a group's score is the sum of its two
+//   largest choice scores (its only one, for groups of one); only experts of the `keep` best groups can be chosen (ties: the lower index);
+//   the `top` largest choices win, weighted with s_e / (sum of the winners' s + 1e-20).
+__device__ __forceinline__ void route_sigmoid_groups(float* __restrict__ zk, float* __restrict__ route_t, int* __restrict__ idx_t, float* __restrict__ w_t,
+                                                     const float* __restrict__ correction, int E, int top, int groups, int keep, int lane) {
+  float* sc = zk + E;
+  float* gs = zk + 2 * E;
+  const int per = E / groups;
+  for (int e = lane; e < E; e += 32) {
+    const float s = 1.f / (1.f + expf(-zk[e]));
+    sc[e] = s;
+    zk[e] = s + (correction != nullptr ? correction[e] : 0.f);
+    route_t[e] = 0.f;
+  }
+  __syncwarp();
+  if (keep < groups) {
+    for (int g = lane; g < groups; g += 32) {
+      float a = -INFINITY, b = -INFINITY;  // largest, second largest
+      for (int e = g * per; e < (g + 1) * per; ++e) {
+        const float v = zk[e];
+        if (v > a) { b = a; a = v; }
+        else if (v > b) b = v;
+      }
+      gs[g] = per > 1 ? a + b : a;
+    }
+    __syncwarp();
+    // the groups that are not kept: all but the `keep` best; a kept group is marked by +inf
+    for (int j = 0; j < keep; ++j) {
+      float best = -INFINITY;
+      int bi = groups;
+      for (int g = lane; g < groups; g += 32)
+        if (gs[g] != INFINITY && (bi == groups || gs[g] > best)) { best = gs[g]; bi = g; }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (oi < groups && (bi == groups || ob > best || (ob == best && oi < bi))) { best = ob; bi = oi; }
+      }
+      if (lane == 0 && bi < groups) gs[bi] = INFINITY;
+      __syncwarp();
+    }
+    for (int e = lane; e < E; e += 32)
+      if (gs[e / per] != INFINITY) zk[e] = -INFINITY;
+    __syncwarp();
+  }
+  float total = 0.f;
+  for (int j = 0; j < top; ++j) {
+    float best = -INFINITY;
+    int bi = E;
+    for (int e = lane; e < E; e += 32)
+      if (!isnan(zk[e]) && (bi == E || zk[e] > best)) { best = zk[e]; bi = e; }  // NaN marks a taken expert
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (oi < E && (bi == E || ob > best || (ob == best && oi < bi))) { best = ob; bi = oi; }
+    }
+    if (bi >= E) bi = 0;  // cannot happen while top <= experts
+    total += sc[bi];
+    if (lane == 0) {
+      idx_t[j] = bi;
+      zk[bi] = __int_as_float(0x7fc00000);
+    }
+    __syncwarp();
+  }
+  const float inv = 1.f / (total + 1e-20f);
+  if (lane == 0)
+    for (int j = 0; j < top; ++j) {
+      const float wv = sc[idx_t[j]] * inv;
+      w_t[j] = wv;
+      route_t[idx_t[j]] = wv;
+    }
+}
+
 template <typename ST, int TOK>
 __global__ void __launch_bounds__(256) moe_router_kernel(float* __restrict__ route, int* __restrict__ top_idx, float* __restrict__ top_w,
-                                                         const ST* __restrict__ h, const float* __restrict__ w_router, int T, int W, int E, int top) {
+                                                         const ST* __restrict__ h, const float* __restrict__ w_router, int T, int W, int E, int top,
+                                                         int zs, int mode, const float* __restrict__ correction, int groups, int keep) {
   // TOK tokens per block (rows h [TOK][W] in shared memory, storage type) and kRouterEPW experts per warp: a router word read from global
   // memory meets TOK rows, a row word read from shared memory meets kRouterEPW experts.  The dot product of a (token, expert) pair is summed
   // in the same order (lane-strided partial sums, then a shuffle tree) whatever else the block holds.  Scores [TOK][E] follow the rows.
@@ -327,13 +403,17 @@ __global__ void __launch_bounds__(256) moe_router_kernel(float* __restrict__ rou
 #pragma unroll
       for (int k = 0; k < TOK; ++k) {
         const float v = warp_sum(d[j][k]);
-        if (lane == 0 && e0 + j < E) z[k * E + e0 + j] = v;
+        if (lane == 0 && e0 + j < E) z[k * zs + e0 + j] = v;
       }
   }
   __syncthreads();
   for (int k = warp; k < nt; k += nw) {  // a warp finishes a token: softmax over all experts, then the `top` largest one by one
     const size_t t = t0 + k;
-    float* zk = z + k * E;
+    float* zk = z + k * zs;
+    if (mode == 1) {
+      route_sigmoid_groups(zk, route + t * E, top_idx + t * top, top_w + t * top, correction, E, top, groups, keep, lane);
+      continue;
+    }
     float mx = -INFINITY;
     for (int e = lane; e < E; e += 32) mx = fmaxf(mx, zk[e]);
     mx = warp_max(mx);
@@ -369,11 +449,11 @@ __global__ void __launch_bounds__(256) moe_router_kernel(float* __restrict__ rou
 }
 
 // Activation of all experts of a token at once.  in row: [F gate | F up] with F = E * ff + ff_shared columns, expert e's at [e ff, (e + 1) ff),
-// the shared expert's last.  g = min(gate, limit), u = clamp(up, -limit, limit), act = g sigmoid(alpha g) (u + 1);
+// the shared expert's last.  g = min(gate, limit), u = clamp(up, -limit, limit), act = g sigmoid(alpha g) (u + shift)  (limit = +inf, alpha = 1, shift = 0: silu(gate) up);
 // out[t][j] = route[t][expert of j] * act (shared columns: weight 1).  An expert that the token does not use contributes exact zeros.
 template <typename ST>
 __global__ void moe_act_kernel(ST* __restrict__ out, const ST* __restrict__ in, const float* __restrict__ route, int E, int ff, float limit,
-                               int ff_shared, float limit_shared, float alpha) {
+                               int ff_shared, float limit_shared, float alpha, float shift) {
   const int t = blockIdx.x;
   const int F = E * ff + ff_shared;
   const int j = blockIdx.y * blockDim.x + threadIdx.x;
@@ -387,7 +467,7 @@ __global__ void moe_act_kernel(ST* __restrict__ out, const ST* __restrict__ in, 
   if (wgt != 0.f) {
     const float g = fminf(ldf(in + (size_t)t * 2 * F + j), lim);
     const float u = fminf(fmaxf(ldf(in + (size_t)t * 2 * F + F + j), -lim), lim);
-    y = wgt * (g / (1.f + expf(-alpha * g))) * (u + 1.f);
+    y = wgt * (g / (1.f + expf(-alpha * g))) * (u + shift);
   }
   stf(out + (size_t)t * F + j, y);
 }
@@ -396,7 +476,7 @@ __global__ void moe_act_kernel(ST* __restrict__ out, const ST* __restrict__ in, 
 // sigmoid(alpha g) = 1 / (1 + 2^(-alpha g log2 e)): one exponential and one division on the special-function unit, far below the rounding of
 // the bfloat16 result
 __global__ void moe_act_bf16x8_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ in, const float* __restrict__ route, int E,
-                                      int ff, float limit, int ff_shared, float limit_shared, float alpha) {
+                                      int ff, float limit, int ff_shared, float limit_shared, float alpha, float shift) {
   const int t = blockIdx.x;
   const int F = E * ff + ff_shared;
   const int j = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
@@ -419,7 +499,7 @@ __global__ void moe_act_bf16x8_kernel(__nv_bfloat16* __restrict__ out, const __n
     u = fminf(fmaxf(u, -lim), lim);
     float e;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(na * g));
-    return wgt * __fdividef(g, 1.f + e) * (u + 1.f);
+    return wgt * __fdividef(g, 1.f + e) * (u + shift);
   };
   st4(o, make_float4(f(g0.x, u0.x), f(g0.y, u0.y), f(g0.z, u0.z), f(g0.w, u0.w)));
   st4(o + 4, make_float4(f(g1.x, u1.x), f(g1.y, u1.y), f(g1.z, u1.z), f(g1.w, u1.w)));
@@ -507,6 +587,100 @@ __global__ void moe_combine_kernel(float* __restrict__ y, const ST* __restrict__
     for (int k = 0; k < top; ++k) a += top_w[t * top + k] * ldf(rows + (size_t)row_of[t * top + k] * W + i);
     y[t * W + i] = a;
   }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------------------
+// Residual update and norm of a plain fp32 stream x [tokens][W].  One block per token:
+//   1. x <- x + add1 + add2 + add_bias      (each may be null; add1 / add2 rows are fp32 or of the storage type, add_bias fp32 [W])
+//   2. (cat_out != null) cat_out[t] <- [x | x0[t]]  in the storage type (the input row of a projection of the stream beside another stream)
+//   3. (out_h != null) kind 1: out_h <- x * rsqrt(mean(x^2) + eps) * w
+//                      kind 2: out_h <- (x - mean) * rsqrt(mean((x - mean)^2) + eps) * w + b       (two passes: mean, then deviations)
+// ---------------------------------------------------------------------------------------------------------------------------------
+template <typename ST>
+__global__ void stream_update_norm_kernel(ST* __restrict__ out_h, ST* __restrict__ cat_out, float* __restrict__ x, const float* __restrict__ x0,
+                                          const void* __restrict__ add1, int add1_f32, const void* __restrict__ add2, int add2_f32,
+                                          const float* __restrict__ add_bias, const float* __restrict__ w, const float* __restrict__ b, int kind,
+                                          float eps, int W) {
+  __shared__ float red[33];
+  const size_t base = (size_t)blockIdx.x * W;
+  float* row = x + base;
+  float sum = 0.f;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    float v = row[i];
+    if (add1 != nullptr || add2 != nullptr || add_bias != nullptr) {
+      float u = 0.f;  // the sublayers' outputs are summed first, then meet the stream
+      if (add1 != nullptr) u += add1_f32 ? static_cast<const float*>(add1)[base + i] : ldf(static_cast<const ST*>(add1) + base + i);
+      if (add2 != nullptr) u += add2_f32 ? static_cast<const float*>(add2)[base + i] : ldf(static_cast<const ST*>(add2) + base + i);
+      if (add_bias != nullptr) u += add_bias[i];
+      v += u;
+      row[i] = v;
+    }
+    if (cat_out != nullptr) {
+      stf(cat_out + 2 * base + i, v);
+      stf(cat_out + 2 * base + W + i, x0[base + i]);
+    }
+    sum += kind == 2 ? v : v * v;
+  }
+  if (out_h == nullptr) return;
+  sum = block_sum(sum, red);
+  float mean = 0.f, r;
+  if (kind == 2) {
+    mean = sum / (float)W;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {  // each thread re-reads what it wrote itself
+      const float d = row[i] - mean;
+      ss += d * d;
+    }
+    ss = block_sum(ss, red);
+    r = 1.f / sqrtf(ss / (float)W + eps);
+  } else {
+    r = 1.f / sqrtf(sum / (float)W + eps);
+  }
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    float v = (row[i] - mean) * r * w[i];
+    if (b != nullptr) v += b[i];
+    stf(out_h + base + i, v);
+  }
+}
+
+// out[t, i] = gelu_tanh(in[t, i] + bias[i])   (bias may be null); rows of in_stride / out_stride elements
+template <typename ST>
+__global__ void bias_gelu_tanh_kernel(ST* __restrict__ out, long long out_stride, const ST* __restrict__ in, long long in_stride,
+                                      const float* __restrict__ bias, int ff) {
+  const int t = blockIdx.x;
+  const int i = blockIdx.y * blockDim.x + threadIdx.x;
+  if (i >= ff) return;
+  const float z = ldf(in + (size_t)t * in_stride + i) + (bias != nullptr ? bias[i] : 0.f);
+  stf(out + (size_t)t * out_stride + i, 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z))));
+}
+
+// bfloat16 rows, eight columns per thread; 0.5 (1 + tanh u) = 1 / (1 + e^(-2u)) on the special-function unit
+__global__ void bias_gelu_tanh_bf16x8_kernel(__nv_bfloat16* __restrict__ out, long long out_stride, const __nv_bfloat16* __restrict__ in,
+                                             long long in_stride, const float* __restrict__ bias, int ff) {
+  const int t = blockIdx.x;
+  const int i = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+  if (i >= ff) return;
+  const __nv_bfloat16* row = in + (size_t)t * in_stride;
+  float4 z0 = ld4(row + i), z1 = ld4(row + i + 4);
+  if (bias != nullptr) {
+    const float4 b0 = ld4(bias + i), b1 = ld4(bias + i + 4);
+    z0.x += b0.x; z0.y += b0.y; z0.z += b0.z; z0.w += b0.w;
+    z1.x += b1.x; z1.y += b1.y; z1.z += b1.z; z1.w += b1.w;
+  }
+  auto f = [](float z) {
+    const float a = 0.7978845608028654f * (z + 0.044715f * z * z * z);
+    float e;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-2.f * 1.4426950408889634f * a));
+    return __fdividef(z, 1.f + e);
+  };
+  st4(out + (size_t)t * out_stride + i, make_float4(f(z0.x), f(z0.y), f(z0.z), f(z0.w)));
+  st4(out + (size_t)t * out_stride + i + 4, make_float4(f(z1.x), f(z1.y), f(z1.z), f(z1.w)));
+}
+
+// x <- cap * tanh(x / cap), fp32 in place
+__global__ void softcap_kernel(float* __restrict__ x, size_t n, float cap) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) x[i] = cap * tanhf(x[i] / cap);
 }
 
 }  // namespace
@@ -612,14 +786,19 @@ int qs_hyb_qk_prepare_append(void* proj, int64_t stride, const float* bias, cons
 }
 
 int qs_hyb_moe_router(float* route, int32_t* top_idx, float* top_w, const void* h, const float* w_router, int tokens_n, int width, int experts,
-                      int top, int dtype, void* stream) {
+                      int top, int mode, const float* correction, int groups, int keep, int dtype, void* stream) {
   QS_REQUIRE(route && top_idx && top_w && h && w_router, "hyb_moe_router: null tensor");
   QS_REQUIRE(experts >= 1 && top >= 1 && top <= experts, "hyb_moe_router: 1 <= top <= experts");
+  QS_REQUIRE(mode == QS_ROUTER_SOFTMAX || mode == QS_ROUTER_SIGMOID_GROUPS, "hyb_moe_router: unknown mode");
+  if (mode == QS_ROUTER_SIGMOID_GROUPS)
+    QS_REQUIRE(groups >= 1 && experts % groups == 0 && keep >= 1 && keep <= groups && top <= keep * (experts / groups),
+               "hyb_moe_router: groups must divide the experts, 1 <= keep <= groups, top <= experts of the kept groups");
+  const int zs = mode == QS_ROUTER_SIGMOID_GROUPS ? 3 * experts : experts;  // floats of work space per token
   if (tokens_n == 0) return qs::QS_OK;
   cudaStream_t s = (cudaStream_t)stream;
   // tokens per block: as many as fit beside their scores in shared memory, at most 8; few tokens (decoding) go one per block
   const size_t es = dtype == QS_DTYPE_BF16 ? 2 : 4;
-  auto bytes = [&](int tk) { return (((size_t)tk * width * es + 15) & ~(size_t)15) + (size_t)tk * experts * sizeof(float); };
+  auto bytes = [&](int tk) { return (((size_t)tk * width * es + 15) & ~(size_t)15) + (size_t)tk * zs * sizeof(float); };
   int tok = tokens_n >= 512 ? 8 : 1;  // every block reads the whole router once (16 tokens per block ran slower: 64 + 16 live accumulators)
   while (tok > 1 && bytes(tok) > 100 * 1024) tok >>= 1;  // two blocks per SM
   const size_t smb = bytes(tok);
@@ -628,7 +807,7 @@ int qs_hyb_moe_router(float* route, int32_t* top_idx, float* top_w, const void* 
   do {                                                                                                                                  \
     if (smb > 48 * 1024) cudaFuncSetAttribute(moe_router_kernel<ST, TOK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smb);       \
     moe_router_kernel<ST, TOK><<<(tokens_n + TOK - 1) / TOK, 256, smb, s>>>(route, top_idx, top_w, (const ST*)h, w_router, tokens_n,   \
-                                                                          width, experts, top);                                        \
+                                                                          width, experts, top, zs, mode, correction, groups, keep);    \
   } while (0)
 #define QS_LAUNCH_T(ST)                          \
   switch (tok) {                                 \
@@ -644,7 +823,7 @@ int qs_hyb_moe_router(float* route, int32_t* top_idx, float* top_w, const void* 
 }
 
 int qs_hyb_moe_act(void* out, const void* in, const float* route, int tokens_n, int experts, int ff, float limit, int ff_shared, float limit_shared,
-                   float alpha, int dtype, void* stream) {
+                   float alpha, float shift, int dtype, void* stream) {
   QS_REQUIRE(out && in && (route || experts == 0), "hyb_moe_act: null tensor");
   QS_REQUIRE(experts >= 0 && ff >= 0 && ff_shared >= 0 && experts * ff + ff_shared > 0, "hyb_moe_act: no columns");
   if (tokens_n == 0) return qs::QS_OK;
@@ -653,14 +832,14 @@ int qs_hyb_moe_act(void* out, const void* in, const float* route, int tokens_n, 
   if (dtype == QS_DTYPE_BF16 && ff % 8 == 0 && ff_shared % 8 == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0 &&
       (reinterpret_cast<uintptr_t>(in) & 15) == 0) {
     moe_act_bf16x8_kernel<<<dim3(tokens_n, (F / 8 + 255) / 256), 256, 0, s>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)in, route, experts, ff, limit,
-                                                                              ff_shared, limit_shared, alpha);
+                                                                              ff_shared, limit_shared, alpha, shift);
     return check_cuda(cudaGetLastError(), "hyb_moe_act");
   }
   dim3 grid(tokens_n, (F + 255) / 256);
   QS_DT(dtype,
         (moe_act_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)in, route, experts, ff, limit, ff_shared,
-                                                             limit_shared, alpha)),
-        (moe_act_kernel<float><<<grid, 256, 0, s>>>((float*)out, (const float*)in, route, experts, ff, limit, ff_shared, limit_shared, alpha)));
+                                                             limit_shared, alpha, shift)),
+        (moe_act_kernel<float><<<grid, 256, 0, s>>>((float*)out, (const float*)in, route, experts, ff, limit, ff_shared, limit_shared, alpha, shift)));
   return check_cuda(cudaGetLastError(), "hyb_moe_act");
 }
 
@@ -700,6 +879,47 @@ int qs_hyb_moe_combine(float* y, const void* rows, const void* shared, const int
         (moe_combine_kernel<__nv_bfloat16><<<tokens_n, threads, 0, s>>>(y, (const __nv_bfloat16*)rows, (const __nv_bfloat16*)shared, row_of, top_w, top, width)),
         (moe_combine_kernel<float><<<tokens_n, threads, 0, s>>>(y, (const float*)rows, (const float*)shared, row_of, top_w, top, width)));
   return check_cuda(cudaGetLastError(), "hyb_moe_combine");
+}
+
+int qs_hyb_stream_update_norm(void* out_h, void* cat_out, float* x, const float* x0, const void* add1, int add1_f32, const void* add2, int add2_f32,
+                              const float* add_bias, const float* w, const float* b, int kind, float eps, int tokens_n, int width, int dtype,
+                              void* stream) {
+  QS_REQUIRE(x, "hyb_stream_update_norm: null stream");
+  QS_REQUIRE(out_h == nullptr || ((kind == QS_NORM_RMS || kind == QS_NORM_LAYER) && w != nullptr), "hyb_stream_update_norm: a norm needs its kind and gain");
+  QS_REQUIRE(cat_out == nullptr || x0 != nullptr, "hyb_stream_update_norm: the joined row needs the second stream");
+  if (tokens_n == 0) return qs::QS_OK;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int threads = width >= 1024 ? 256 : 128;
+  QS_DT(dtype,
+        (stream_update_norm_kernel<__nv_bfloat16><<<tokens_n, threads, 0, s>>>((__nv_bfloat16*)out_h, (__nv_bfloat16*)cat_out, x, x0, add1, add1_f32, add2,
+                                                                                add2_f32, add_bias, w, b, kind, eps, width)),
+        (stream_update_norm_kernel<float><<<tokens_n, threads, 0, s>>>((float*)out_h, (float*)cat_out, x, x0, add1, add1_f32, add2, add2_f32, add_bias, w, b,
+                                                                       kind, eps, width)));
+  return check_cuda(cudaGetLastError(), "hyb_stream_update_norm");
+}
+
+int qs_hyb_bias_gelu_tanh(void* out, int64_t out_stride, const void* in, int64_t in_stride, const float* bias, int tokens_n, int ff, int dtype,
+                          void* stream) {
+  QS_REQUIRE(out && in, "hyb_bias_gelu_tanh: null tensor");
+  if (tokens_n == 0) return qs::QS_OK;
+  cudaStream_t s = (cudaStream_t)stream;
+  auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  if (dtype == QS_DTYPE_BF16 && ff % 8 == 0 && out_stride % 8 == 0 && in_stride % 8 == 0 && al16(out) && al16(in) && al16(bias)) {
+    bias_gelu_tanh_bf16x8_kernel<<<dim3(tokens_n, (ff / 8 + 255) / 256), 256, 0, s>>>((__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)in, in_stride,
+                                                                                     bias, ff);
+    return check_cuda(cudaGetLastError(), "hyb_bias_gelu_tanh");
+  }
+  dim3 grid(tokens_n, (ff + 255) / 256);
+  QS_DT(dtype, (bias_gelu_tanh_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)in, in_stride, bias, ff)),
+        (bias_gelu_tanh_kernel<float><<<grid, 256, 0, s>>>((float*)out, out_stride, (const float*)in, in_stride, bias, ff)));
+  return check_cuda(cudaGetLastError(), "hyb_bias_gelu_tanh");
+}
+
+int qs_hyb_softcap(float* x, int64_t n, float cap, void* stream) {
+  QS_REQUIRE(x && cap > 0.f, "hyb_softcap: null tensor or cap <= 0");
+  if (n == 0) return qs::QS_OK;
+  softcap_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(x, (size_t)n, cap);
+  return check_cuda(cudaGetLastError(), "hyb_softcap");
 }
 
 }  // extern "C"

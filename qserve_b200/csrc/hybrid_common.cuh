@@ -70,5 +70,13 @@ __device__ __forceinline__ void cp_async4(float* dst, const float* src) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
 }
 
+// first position a query at `pos` sees: the start of its chunk of `chunk` positions (0: no chunks), and not further back than `window`
+// positions including its own (0: no window)
+__host__ __device__ __forceinline__ int first_key(int pos, int chunk, int window) {
+  int f = chunk > 0 ? pos - pos % chunk : 0;
+  if (window > 0) f = max(f, pos - window + 1);
+  return f;
+}
+
 }  // namespace hyb
 }  // namespace qs

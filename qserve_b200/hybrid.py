@@ -21,10 +21,26 @@ import torch
 
 from ._lib import check, lib
 from .cache import HybridCache
-from .modelcfg import (AttentionMixerConfig, DeltaMixerConfig, GateRecurrenceMixerConfig, HybridConfig, MlpConfig, MoeConfig, ParallelMixerConfig,
-                       RetentionMixerConfig)
+from .modelcfg import (AttentionMixerConfig, DeltaMixerConfig, GateRecurrenceMixerConfig, HybridConfig, LatentAttentionMixerConfig, MlpConfig,
+                       MoeConfig, ParallelMixerConfig, RetentionMixerConfig)
 
 _DT = {torch.bfloat16: 0, torch.float32: 1}
+_NORM_KIND = {"rms": 1, "layer": 2}      # QS_NORM_RMS, QS_NORM_LAYER
+_ROUTER_MODE = {"softmax": 0, "sigmoid": 1}  # QS_ROUTER_SOFTMAX, QS_ROUTER_SIGMOID_GROUPS
+_F32_OUT = [None]  # whether torch.mm takes out_dtype on this build (found at first use)
+
+
+def _mm_f32(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """a @ b with an fp32 result (the accumulator as it is, where the library offers it; else the storage type's rounding widened)."""
+    if a.dtype == torch.float32:
+        return torch.mm(a, b)
+    if _F32_OUT[0] is None:
+        try:
+            torch.mm(a[:1], b, out_dtype=torch.float32)
+            _F32_OUT[0] = True
+        except (TypeError, RuntimeError):
+            _F32_OUT[0] = False
+    return torch.mm(a, b, out_dtype=torch.float32) if _F32_OUT[0] else torch.mm(a, b).float()
 
 
 def _stream(dev: torch.device):
@@ -296,6 +312,71 @@ class RetentionMixer(_Mixer):
                                    _p(b.entry_slot), _p(b.entry_pos0), T, b.n_entries, m.heads, m.dim, m.vdim, self.eps, dt, stream))
 
 
+class LatentAttentionMixer(_Mixer):
+    """Latent attention: c_q = unit_rms(W_dq h) g_q, q = W_uq c_q (per head `dim` unrotated and `rot_dim` rotated numbers); [c | k_rot] =
+    [unit_rms((W_dkv h)[:kv_rank]) g_kv | rotate((W_dkv h)[kv_rank:])] is all the cache holds per position.  Scores
+    (q_nope . W_uk c + q_rot . k_rot) * scale are formed as (W_uk^T q_nope) . c + q_rot . k_rot: the key up-projection is applied to the
+    query (a batched product over the heads), every head scores the cached rows as they lie in memory, the weighted sum of the latents goes
+    through the value up-projection W_uv (another batched product), and a sigmoid gate of the mixer's input scales each head."""
+
+    def __init__(self, m: LatentAttentionMixerConfig, w: Dict[str, torch.Tensor], eps: float, dtype, device):
+        self.m, self.eps = m, eps
+        H, D, R, Dv, K, Q = m.heads, m.dim, m.rot_dim, m.vdim, m.kv_rank, m.q_rank
+        names = (("dq", Q), ("uq", H * (D + R)), ("dkv", K + R), ("uk", H * D), ("uv", H * Dv)) + ((("g", H),) if m.gate else ())
+        for name, rows in names:
+            if w[name].shape[0] != rows:
+                raise ValueError(f"latent attention weight {name}: {tuple(w[name].shape)} does not have {rows} rows")
+        if w["uq"].shape[1] != Q or w["uk"].shape[1] != K or w["uv"].shape[1] != K or w["dq.norm"].numel() != Q or w["dkv.norm"].numel() != K:
+            raise ValueError("latent attention: up-projections and gains do not match q_rank / kv_rank")
+        st = lambda t: t.to(device=device, dtype=dtype).contiguous()
+        f32 = lambda t: t.to(torch.float32).to(device).contiguous()
+        # one product makes [query latent | key/value latent, rotated key part | gate logits]
+        self.col_q, self.col_kv, self.col_g = 0, Q, Q + K + R
+        self.in_features = Q + K + R + (H if m.gate else 0)
+        self.out_features = H * Dv
+        self.w_in = st(torch.cat([w["dq"], w["dkv"]] + ([w["g"]] if m.gate else []), 0))
+        self.w_uq = st(w["uq"])
+        self.w_uk = st(w["uk"]).view(H, D, K)                                   # q_lat[h] = q_nope[h] @ w_uk[h]
+        self.w_uv = st(w["uv"].reshape(H, Dv, K).transpose(1, 2))               # [H, K, Dv]: values[h] = o_lat[h] @ w_uv[h]
+        self.w_out = w["o"]
+        self.gain_q, self.gain_kv = f32(w["dq.norm"]), f32(w["dkv.norm"])
+        if m.rot is not None and (m.rot.layout != "half" or m.rot.factor is not None):
+            raise ValueError("latent attention rotates pairs (i, i + dims/2) with unscaled frequencies")
+        self.inv_freq = torch.tensor(m.rot.inv_freq(), dtype=torch.float64).to(torch.float32).to(device) if m.rot is not None else None
+        self.rot_dims = m.rot.dims if m.rot is not None else 0
+
+    def scratch_floats(self, tokens: int) -> int:
+        return int(lib.qs_hyb_latent_attention_scratch_floats(tokens, self.m.heads, self.m.kv_rank))
+
+    def run(self, proj: torch.Tensor, out: torch.Tensor, b: StepBatch, run_cache: dict, page_size: int, scratch, dt: int, stream) -> None:
+        m, T, dev = self.m, b.n_tokens, proj.device
+        H, D, R, Dv, K, Q = m.heads, m.dim, m.rot_dim, m.vdim, m.kv_rank, m.q_rank
+        pool = run_cache["c"]
+        cq = torch.empty((T, Q), dtype=proj.dtype, device=dev)
+        check(lib.qs_hyb_latent_prepare(cq.data_ptr(), proj.data_ptr(), proj.stride(0), self.col_q, self.col_kv, self.gain_q.data_ptr(),
+                                        self.gain_kv.data_ptr(), _p(self.inv_freq), self.rot_dims, _p(b.tok_slot), _p(b.tok_pos), _p(b.block_table),
+                                        b.block_table.shape[1], pool.data_ptr(), T, Q, K, R, page_size, self.eps, dt, stream))
+        q = torch.mm(cq, self.w_uq.t())                                          # [T, H (D + R)]
+        qlat = torch.bmm(q.view(T, H, D + R)[:, :, :D].transpose(0, 1), self.w_uk)  # [H, T, K]
+        qa = torch.empty((T, H, K + R), dtype=proj.dtype, device=dev)
+        check(lib.qs_hyb_latent_query(qa.data_ptr(), qlat.data_ptr(), q.data_ptr(), q.stride(0), _p(self.inv_freq), self.rot_dims, _p(b.tok_pos), T, H,
+                                      D, K, R, dt, stream))
+        olat = torch.empty((H, T, K), dtype=proj.dtype, device=dev)
+        if scratch is not None and LATENT_IMPL != "plain" and lib.qs_hyb_latent_attention_fast_supported(dt, H, K, R) == 1:
+            check(lib.qs_hyb_latent_attention_fast(olat.data_ptr(), qa.data_ptr(), pool.data_ptr(), _p(b.tok_slot), _p(b.tok_pos), _p(b.block_table),
+                                                   b.block_table.shape[1], _p(b.entry_start), _p(b.entry_len), _p(b.entry_slot), _p(b.entry_pos0),
+                                                   b.n_entries, T, scratch.data_ptr(), H, K, R, m.scale, page_size, m.chunk, m.window, dt, stream))
+        else:
+            check(lib.qs_hyb_latent_attention(olat.data_ptr(), qa.data_ptr(), pool.data_ptr(), _p(b.tok_slot), _p(b.tok_pos), _p(b.block_table),
+                                              b.block_table.shape[1], T, H, K, R, m.scale, page_size, m.chunk, m.window, dt, stream))
+        ov = torch.bmm(olat, self.w_uv)                                          # [H, T, Dv]
+        check(lib.qs_hyb_latent_gate_out(out.data_ptr(), out.stride(0), ov.data_ptr(), proj.data_ptr() if m.gate else None, proj.stride(0), self.col_g,
+                                         T, H, Dv, dt, stream))
+
+
+LATENT_IMPL = None  # tests: "plain" keeps the latent attention on the CUDA-core kernel
+
+
 class ParallelMixer(_Mixer):
     """Two mixers on the same input: one product makes both projection rows, each runs on its part, and the result is
     scale (norm(W_o,left heads_left) gain_left + norm(W_o,right heads_right) gain_right) with plain RMS norms over the width."""
@@ -338,7 +419,7 @@ class ParallelMixer(_Mixer):
 
 
 MIXERS = {AttentionMixerConfig: MultiMapAttentionMixer, DeltaMixerConfig: GatedDeltaMixer, GateRecurrenceMixerConfig: GateRecurrenceMixer,
-          RetentionMixerConfig: RetentionMixer, ParallelMixerConfig: ParallelMixer}
+          RetentionMixerConfig: RetentionMixer, ParallelMixerConfig: ParallelMixer, LatentAttentionMixerConfig: LatentAttentionMixer}
 
 
 # ------------------------------------------------------------------------------------------------------------------------
@@ -348,8 +429,8 @@ MOE_IMPL = None  # tests: force "sorted" or "dense"; None picks by storage type 
 
 
 class MoeFeedForward:
-    """Mixture of experts with an optional shared expert.  The router (fp32 logits, softmax, top scores) is one kernel.  Two ways to run the
-    experts:
+    """Mixture of experts with an optional shared expert.  The router (fp32 logits; softmax scores, or sigmoid scores with a correction and
+    groups of experts; the best `top`) is one kernel.  Two ways to run the experts:
 
     "sorted": the (token, chosen expert) pairs are sorted by expert on the device (every expert's rows in token order), the tokens' rows are
               gathered in that order, two grouped matrix products (one group per expert) make gate | up and the down projection, and a kernel
@@ -386,6 +467,11 @@ class MoeFeedForward:
         self.w_router = w["router"].to(torch.float32).to(device).contiguous()
         if tuple(self.w_router.shape) != (c.experts, width):
             raise ValueError("router weight is not [experts, width]")
+        if c.router not in _ROUTER_MODE:
+            raise ValueError(f"unknown router {c.router!r}")
+        self.correction = w["correction"].to(torch.float32).to(device).contiguous() if c.correction else None
+        if self.correction is not None and self.correction.numel() != c.experts:
+            raise ValueError("the router's correction has one number per expert")
 
     def run(self, h: torch.Tensor, dt: int, stream):
         """h [T, W] (storage type) -> (rows [T, W], rows are fp32)."""
@@ -395,12 +481,12 @@ class MoeFeedForward:
         top_idx = torch.empty((T, c.top), dtype=torch.int32, device=dev)
         top_w = torch.empty((T, c.top), dtype=torch.float32, device=dev)
         check(lib.qs_hyb_moe_router(route.data_ptr(), top_idx.data_ptr(), top_w.data_ptr(), h.data_ptr(), self.w_router.data_ptr(), T, W, c.experts,
-                                    c.top, dt, stream))
+                                    c.top, _ROUTER_MODE[c.router], _p(self.correction), c.groups, c.keep, dt, stream))
         if self.impl == "dense":
             gu = torch.mm(h, self.w_in.t())
             act = torch.empty((T, self.F), dtype=h.dtype, device=dev)
             check(lib.qs_hyb_moe_act(act.data_ptr(), gu.data_ptr(), route.data_ptr(), T, c.experts, c.ff, c.limit, c.shared_ff, c.shared_limit, c.alpha,
-                                     dt, stream))
+                                     c.up_shift, dt, stream))
             return torch.mm(act, self.w_down.t()), False
         n = T * c.top
         ends = torch.empty(c.experts, dtype=torch.int32, device=dev)
@@ -412,13 +498,13 @@ class MoeFeedForward:
         check(lib.qs_hyb_moe_gather(xs.data_ptr(), h.data_ptr(), src.data_ptr(), n, W, dt, stream))
         gu = torch.nn.functional.grouped_mm(xs, self.w_gu.transpose(-2, -1), offs=ends)
         act = torch.empty((n, c.ff), dtype=h.dtype, device=dev)
-        check(lib.qs_hyb_moe_act(act.data_ptr(), gu.data_ptr(), None, n, 0, 0, 0.0, c.ff, c.limit, c.alpha, dt, stream))
+        check(lib.qs_hyb_moe_act(act.data_ptr(), gu.data_ptr(), None, n, 0, 0, 0.0, c.ff, c.limit, c.alpha, c.up_shift, dt, stream))
         rows = torch.nn.functional.grouped_mm(act, self.w_dn.transpose(-2, -1), offs=ends)
         shared = None
         if c.shared_ff:
             gs = torch.mm(h, self.w_sh_in.t())
             sa = torch.empty((T, c.shared_ff), dtype=h.dtype, device=dev)
-            check(lib.qs_hyb_moe_act(sa.data_ptr(), gs.data_ptr(), None, T, 0, 0, 0.0, c.shared_ff, c.shared_limit, c.alpha, dt, stream))
+            check(lib.qs_hyb_moe_act(sa.data_ptr(), gs.data_ptr(), None, T, 0, 0, 0.0, c.shared_ff, c.shared_limit, c.alpha, c.up_shift, dt, stream))
             shared = torch.mm(sa, self.w_sh_dn.t())
         y = torch.empty((T, W), dtype=torch.float32, device=dev)
         check(lib.qs_hyb_moe_combine(y.data_ptr(), rows.data_ptr(), _p(shared), row_of.data_ptr(), top_w.data_ptr(), T, c.top, W, dt, stream))
@@ -458,6 +544,11 @@ class _Layer:
     def __init__(self, mixer, norm1, norm2, w_mlp_in, w_out, ff, hc1=None, hc2=None):
         self.mixer, self.norm1, self.norm2, self.w_mlp_in, self.w_out, self.ff = mixer, norm1, norm2, w_mlp_in, w_out, ff
         self.hc1, self.hc2 = hc1, hc2
+        # parallel blocks: norm biases (layer norms), a dense feed-forward folded into the block's products (ff columns, gated or not, biases of
+        # its projections), or a feed-forward that runs by itself beside the mixer (mixture of experts)
+        self.norm1_b = self.norm2_b = self.mlp_in_bias = self.out_bias = self.side_ff = None
+        self.w_all_in = None  # mixer and feed-forward input projections stacked (blocks whose branches read one normed row)
+        self.gated = True
 
 
 class HybridDecoder:
@@ -519,14 +610,51 @@ class HybridDecoder:
                 continue
             outs = [mixer.w_out]
             w_mlp_in, norm2, ff = None, None, 0
-            if ly.mlp is not None:
+            dense = isinstance(ly.mlp, MlpConfig)
+            if dense:  # folded: its activation sits beside the mixer's heads as input of ONE output product
                 ff = ly.mlp.ff
-                w_mlp_in = st(torch.cat([weights[pre + "mlp.gate"], weights[pre + "mlp.up"]], 0))
+                w_mlp_in = st(torch.cat([weights[pre + "mlp.gate"], weights[pre + "mlp.up"]], 0) if ly.mlp.gated else weights[pre + "mlp.up"])
+                if tuple(w_mlp_in.shape) != ((2 if ly.mlp.gated else 1) * ff, W) or tuple(weights[pre + "mlp.down"].shape) != (W, ff):
+                    raise ValueError(f"{pre}mlp: the projections do not match ff x width")
                 outs.append(weights[pre + "mlp.down"])
+            if ly.mlp is not None and not cfg.shared_norm:
                 norm2 = f32(weights[pre + "norm2"])
             w_out = st(torch.cat(outs, 1))  # [W, heads*vdim + ff]
             del mixer.w_out
-            self.layers.append(_Layer(mixer, f32(weights[pre + "norm1"]), norm2, w_mlp_in, w_out, ff))
+            layer = _Layer(mixer, f32(weights[pre + "norm1"]), norm2, w_mlp_in, w_out, ff)
+            if cfg.norm_kind == "layer":
+                layer.norm1_b = f32(weights[pre + "norm1.b"])
+                layer.norm2_b = f32(weights[pre + "norm2.b"]) if norm2 is not None else None
+            if dense:
+                layer.gated = ly.mlp.gated
+                if ly.mlp.bias:
+                    if ly.mlp.gated:
+                        layer.mlp_in_bias = f32(torch.cat([weights[pre + "mlp.gate.b"], weights[pre + "mlp.up.b"]], 0))
+                    else:
+                        layer.mlp_in_bias = f32(weights[pre + "mlp.up.b"])
+                    layer.out_bias = f32(weights[pre + "mlp.down.b"])
+                    if layer.mlp_in_bias.numel() != w_mlp_in.shape[0] or layer.out_bias.numel() != W:
+                        raise ValueError(f"{pre}mlp: the biases do not match their projections")
+                if ly.mlp.gated and ly.mlp.bias:
+                    raise NotImplementedError("a gated dense feed-forward with biases")
+            elif ly.mlp is not None:
+                fw = {k[len(pre) + 4:]: v for k, v in weights.items() if k.startswith(pre + "mlp.")}
+                layer.side_ff = FEED_FORWARDS[type(ly.mlp)](ly.mlp, fw, W, dtype, dev)
+            if dense and cfg.shared_norm and not ly.mlp.gated:
+                layer.w_all_in = torch.cat([mixer.w_in, w_mlp_in], 0).contiguous()
+                del mixer.w_in
+                layer.w_mlp_in = None
+            self.layers.append(layer)
+        if cfg.norm_kind not in _NORM_KIND:
+            raise ValueError(f"unknown norm {cfg.norm_kind!r}")
+        if cfg.norm_kind == "layer" and (cfg.block != "parallel" or cfg.norm_offset != 0.0 or cfg.norm_groups != 1):
+            raise NotImplementedError("layer norms are built for parallel blocks with plain gains")
+        self.final_norm_b = f32(weights["final.norm.b"]) if cfg.norm_kind == "layer" else None
+        self.loop_in = None
+        if cfg.loop_in:
+            self.loop_in = st(weights["loop.in"])
+            if tuple(self.loop_in.shape) != (W, 2 * W):
+                raise ValueError("loop.in must be [width, 2 width]")
         self.schedule = cfg.schedule()
         self._scratch: Optional[torch.Tensor] = None
 
@@ -561,26 +689,64 @@ class HybridDecoder:
             scratch = self._scratch
         if cfg.block == "sequential":
             return self._forward_sequential(x, b, cache, tap, scratch, s)
+        return self._forward_parallel(x, b, cache, tap, scratch, s)
+
+    def _land(self, x, pending, s, out_h=None, w=None, bias=None, cat_out=None, x0=None) -> None:
+        """x <- x + the pending sublayer outputs (rows, rows are fp32, second rows, they are fp32, a bias row); then the norm of x into out_h and /
+        or [x | x0] into cat_out."""
+        a1, f1, a2, f2, ab = pending if pending is not None else (None, False, None, False, None)
+        check(lib.qs_hyb_stream_update_norm(_p(out_h), _p(cat_out), x.data_ptr(), _p(x0), _p(a1), 1 if f1 else 0, _p(a2), 1 if f2 else 0, _p(ab), _p(w),
+                                            _p(bias), _NORM_KIND[self.cfg.norm_kind] if out_h is not None else 0, self.cfg.eps, x.shape[0],
+                                            self.cfg.width, self.dt, s))
+
+    def _forward_parallel(self, x, b: StepBatch, cache: HybridCache, tap, scratch, s) -> torch.Tensor:
+        cfg, dev, dt, T, W = self.cfg, self.device, self.dt, b.n_tokens, self.cfg.width
         h1 = torch.empty((T, W), dtype=self.dtype, device=dev)
-        h2 = torch.empty((T, W), dtype=self.dtype, device=dev)
-        upd = None  # the previous layer's update, still to be added to the stream
+        h2 = h1 if cfg.shared_norm else torch.empty((T, W), dtype=self.dtype, device=dev)
+        starts = set(cfg.pass_starts()) if self.loop_in is not None else set()
+        x0 = x.clone() if starts else None  # the embedding output, read again at the start of every pass
+        # the outputs of the previous layer still to be added to the stream: they land inside the next kernel that reads it (one pass over x)
+        pending = None
         for run, li in enumerate(self.schedule):
             ly = self.layers[li]
-            # the stream takes the previous layer's update inside this layer's norm kernel (one pass over x instead of two)
-            check(lib.qs_hyb_rms_norm(h1.data_ptr(), _p(h2) if ly.ff else None, x.data_ptr(), _p(upd) if tap is None else None, ly.norm1.data_ptr(),
-                                      _p(ly.norm2), cfg.norm_offset, cfg.eps, T, W, dt, s))
-            proj = torch.mm(h1, ly.mixer.w_in.t())
+            if run in starts:  # x <- W_in [x; x0]
+                xin = torch.empty((T, 2 * W), dtype=self.dtype, device=dev)
+                self._land(x, pending, s, cat_out=xin, x0=x0)
+                pending = None
+                x = _mm_f32(xin, self.loop_in.t())
+            has_ff = ly.ff > 0 or ly.side_ff is not None
+            plain = pending is None or (pending[2] is None and pending[4] is None and not pending[1])
+            if cfg.norm_kind == "rms" and not cfg.shared_norm and plain:
+                check(lib.qs_hyb_rms_norm(h1.data_ptr(), _p(h2) if has_ff else None, x.data_ptr(), _p(pending[0]) if pending else None,
+                                          ly.norm1.data_ptr(), _p(ly.norm2), cfg.norm_offset, cfg.eps, T, W, dt, s))
+            else:
+                self._land(x, pending, s, out_h=h1, w=ly.norm1, bias=ly.norm1_b)
+                if has_ff and not cfg.shared_norm:
+                    self._land(x, None, s, out_h=h2, w=ly.norm2, bias=ly.norm2_b)
+            if ly.w_all_in is not None:
+                # one product for the mixer's projections and the feed-forward's: both read the same normed row
+                both = torch.mm(h1, ly.w_all_in.t())
+                proj, gu = both[:, :ly.mixer.in_features], both[:, ly.mixer.in_features:]
+            else:
+                proj = torch.mm(h1, ly.mixer.w_in.t())
+                gu = torch.mm(h2, ly.w_mlp_in.t()) if ly.ff else None
             cat = torch.empty((T, ly.mixer.out_features + ly.ff), dtype=self.dtype, device=dev)
-            ly.mixer.run(proj, cat, b, cache.runs[run], cache.page_size, scratch, dt, s)
+            ly.mixer.run(proj, cat[:, :ly.mixer.out_features] if ly.ff else cat, b, cache.runs[run], cache.page_size, scratch, dt, s)
             if ly.ff:
-                gu = torch.mm(h2, ly.w_mlp_in.t())
-                check(lib.qs_hyb_gelu_tanh_mul(cat.data_ptr() + ly.mixer.out_features * cat.element_size(), cat.stride(0), gu.data_ptr(), T, ly.ff, dt, s))
+                act = cat.data_ptr() + ly.mixer.out_features * cat.element_size()
+                if ly.gated:
+                    check(lib.qs_hyb_gelu_tanh_mul(act, cat.stride(0), gu.data_ptr(), T, ly.ff, dt, s))
+                else:
+                    check(lib.qs_hyb_bias_gelu_tanh(act, cat.stride(0), gu.data_ptr(), gu.stride(0), _p(ly.mlp_in_bias), T, ly.ff, dt, s))
             upd = torch.mm(cat, ly.w_out.t())
+            side, side32 = ly.side_ff.run(h2, dt, s) if ly.side_ff is not None else (None, False)
+            pending = (upd, False, side, side32, ly.out_bias)
             if tap is not None:  # observers want the stream after every run: add right away
-                check(lib.qs_hyb_residual_add(x.data_ptr(), upd.data_ptr(), T * W, dt, s))
+                self._land(x, pending, s)
+                pending = None
                 tap(run, x)
-        if upd is not None and tap is None:
-            check(lib.qs_hyb_residual_add(x.data_ptr(), upd.data_ptr(), T * W, dt, s))
+        if pending is not None:
+            self._land(x, pending, s)
         return x
 
     def _stream_norm(self, out_h, out_sum, x, pending, cin, w, s) -> None:
@@ -625,9 +791,16 @@ class HybridDecoder:
             check(lib.qs_hyb_stream_norm(h.data_ptr(), None, x_rows.data_ptr(), 1, None, 0, None, None, None, self.final_norm.data_ptr(),
                                          self.cfg.norm_groups, self.cfg.norm_offset, self.cfg.eps, n, W, self.dt, _stream(self.device)))
             return torch.mm(h, self.head.t()).float()
-        check(lib.qs_hyb_rms_norm(h.data_ptr(), None, x_rows.data_ptr(), None, self.final_norm.data_ptr(), None, self.cfg.norm_offset, self.cfg.eps, n, W,
-                                  self.dt, _stream(self.device)))
-        return torch.mm(h, self.head.t()).float()
+        s = _stream(self.device)
+        if self.cfg.norm_kind == "rms":
+            check(lib.qs_hyb_rms_norm(h.data_ptr(), None, x_rows.data_ptr(), None, self.final_norm.data_ptr(), None, self.cfg.norm_offset, self.cfg.eps, n,
+                                      W, self.dt, s))
+        else:
+            self._land(x_rows, None, s, out_h=h, w=self.final_norm, bias=self.final_norm_b)
+        out = _mm_f32(h, self.head.t()) if self.cfg.logit_softcap > 0.0 else torch.mm(h, self.head.t()).float()
+        if self.cfg.logit_softcap > 0.0:
+            check(lib.qs_hyb_softcap(out.data_ptr(), out.numel(), self.cfg.logit_softcap, s))
+        return out
 
 
 def random_weights(cfg: HybridConfig, seed: int = 0, device: Optional[torch.device] = None, dtype: torch.dtype = torch.bfloat16) -> Dict[str, torch.Tensor]:
@@ -647,7 +820,14 @@ def random_weights(cfg: HybridConfig, seed: int = 0, device: Optional[torch.devi
             w[p + "left.out"], w[p + "right.out"] = 1.0 + r(W, s=0.1), 1.0 + r(W, s=0.1)
             return
         H, D, Dv = m.heads, m.dim, m.vdim
-        if isinstance(m, AttentionMixerConfig):
+        if isinstance(m, LatentAttentionMixerConfig):
+            K, Q, R = m.kv_rank, m.q_rank, m.rot_dim
+            w[p + "dq"], w[p + "dq.norm"], w[p + "uq"] = r(Q, W, s=W ** -0.5), 1.0 + r(Q, s=0.1), r(H * (D + R), Q, s=Q ** -0.5)
+            w[p + "dkv"], w[p + "dkv.norm"] = r(K + R, W, s=W ** -0.5), 1.0 + r(K, s=0.1)
+            w[p + "uk"], w[p + "uv"] = r(H * D, K, s=K ** -0.5), r(H * Dv, K, s=K ** -0.5)
+            if m.gate:
+                w[p + "g"] = r(H, W, s=W ** -0.5)
+        elif isinstance(m, AttentionMixerConfig):
             G = m.kv_heads
             w[p + "q"], w[p + "k"], w[p + "v"] = r(H * m.maps * D, W, s=W ** -0.5), r(G * m.maps * D, W, s=W ** -0.5), r(G * Dv, W, s=W ** -0.5)
             if m.maps == 2:
@@ -679,22 +859,38 @@ def random_weights(cfg: HybridConfig, seed: int = 0, device: Optional[torch.devi
 
     gain = (lambda: 1.0 + r(W, s=0.1)) if cfg.norm_offset == 0.0 else (lambda: r(W, s=0.1))
     w = {"embed": r(cfg.vocab, W), "head": r(cfg.vocab, W, s=W ** -0.5), "final.norm": gain()}
+    layer_norm = cfg.norm_kind == "layer"
+    if layer_norm:
+        w["final.norm.b"] = r(W, s=0.1)
+    if cfg.loop_in:
+        w["loop.in"] = r(W, 2 * W, s=(2 * W) ** -0.5)
     if cfg.pair_buckets:
         w["bigram"] = r(cfg.pair_buckets + 1, W, s=0.5)
     for i, ly in enumerate(cfg.layers):
         p = f"l{i}."
         w[p + "norm1"] = gain()
         mixer_weights(p + "mix.", ly.mixer)
+        if layer_norm:
+            w[p + "norm1.b"] = r(W, s=0.1)
         if ly.mlp is not None:
-            w[p + "norm2"] = gain()
+            if not cfg.shared_norm:
+                w[p + "norm2"] = gain()
+                if layer_norm:
+                    w[p + "norm2.b"] = r(W, s=0.1)
             if isinstance(ly.mlp, MoeConfig):
                 c = ly.mlp
                 for n in [f"e{e}" for e in range(c.experts)] + (["shared"] if c.shared_ff else []):
                     ff = c.shared_ff if n == "shared" else c.ff
                     w[f"{p}mlp.{n}.gate"], w[f"{p}mlp.{n}.up"], w[f"{p}mlp.{n}.down"] = r(ff, W, s=W ** -0.5), r(ff, W, s=W ** -0.5), r(W, ff, s=ff ** -0.5)
                 w[p + "mlp.router"] = r(c.experts, W, s=W ** -0.5)
+                if c.correction:
+                    w[p + "mlp.correction"] = r(c.experts, s=0.1)
             else:
-                w[p + "mlp.gate"], w[p + "mlp.up"], w[p + "mlp.down"] = r(ly.mlp.ff, W, s=W ** -0.5), r(ly.mlp.ff, W, s=W ** -0.5), r(W, ly.mlp.ff, s=ly.mlp.ff ** -0.5)
+                w[p + "mlp.up"], w[p + "mlp.down"] = r(ly.mlp.ff, W, s=W ** -0.5), r(W, ly.mlp.ff, s=ly.mlp.ff ** -0.5)
+                if ly.mlp.gated:
+                    w[p + "mlp.gate"] = r(ly.mlp.ff, W, s=W ** -0.5)
+                if ly.mlp.bias:
+                    w[p + "mlp.up.b"], w[p + "mlp.down.b"] = r(ly.mlp.ff, s=0.1), r(W, s=0.1)
         if cfg.streams > 0:
             ns = cfg.streams
             for q in (1, 2) if ly.mlp is not None else (1,):

@@ -136,16 +136,42 @@ class DeltaMixerConfig:
 
 
 @dataclass(frozen=True)
+class LatentAttentionMixerConfig:
+    """Causal softmax attention whose keys and values are linear images of a small latent row per position: only that row (`kv_rank` numbers,
+    unit RMS times a gain) and one rotated key part of `rot_dim` numbers shared by all heads are cached.  Queries pass a latent of `q_rank`
+    numbers (unit RMS times a gain); a head's query has `dim` unrotated and `rot_dim` rotated numbers, its value `vdim`.  `gate`: every head's
+    output is multiplied by the sigmoid of a projection of the mixer's input (one number per head)."""
+    heads: int
+    dim: int
+    rot_dim: int
+    vdim: int
+    kv_rank: int
+    q_rank: int
+    rot: Optional[RotaryConfig]
+    scale: float
+    gate: bool = True
+    chunk: int = 0
+    window: int = 0
+
+
+@dataclass(frozen=True)
 class MlpConfig:
+    """Dense feed-forward.  gated: W_down(gelu_tanh(W_gate h) * W_up h); not gated: W_down gelu_tanh(W_up h).  bias: every projection has one."""
     kind: str
     ff: int
+    gated: bool = True
+    bias: bool = False
 
 
 @dataclass(frozen=True)
 class MoeConfig:
-    """Mixture of experts: softmax router over `experts`, the `top` best run, weighted by their scores as they are; experts compute
-    W_down(g sigmoid(alpha g) (u + 1)) with g = min(W_gate h, limit), u = clamp(W_up h, -limit, limit); optionally a shared expert for every
-    token with its own size and limit."""
+    """Mixture of experts: the `top` best of `experts` run per token; experts compute W_down(g sigmoid(alpha g) (u + up_shift)) with
+    g = min(W_gate h, limit), u = clamp(W_up h, -limit, limit) (limit = inf, alpha = 1, up_shift = 0: silu(W_gate h) * W_up h); optionally a
+    shared expert for every token with its own size and limit.
+    router "softmax": scores softmax over all experts, the winners weighted by their scores as they are.
+    router "sigmoid": scores sigmoid(logit); the choice is made on score + a learned correction per expert (tensor `correction`), restricted
+    to the `keep` best of `groups` equal groups of neighbouring experts (a group's score: the sum of its two largest choice scores); the
+    winners are weighted by their scores divided by the winners' sum."""
     experts: int
     top: int
     ff: int
@@ -154,6 +180,11 @@ class MoeConfig:
     shared_limit: float = 0.0
     alpha: float = 1.702
     kind: str = "moe"
+    up_shift: float = 1.0
+    router: str = "softmax"
+    correction: bool = False
+    groups: int = 1
+    keep: int = 1
 
 
 @dataclass(frozen=True)
@@ -181,11 +212,20 @@ class HybridConfig:
     streams: int = 0          # sequential blocks: > 0 = that many residual streams with hyper-connection coefficients (tensors hc1.*, hc2.*)
     norm_groups: int = 1      # RMS norms work on this many equal consecutive parts of the width, each with its own statistic
     embed_scale: float = 1.0
+    norm_kind: str = "rms"    # "layer": (x - mean) / sqrt(var + eps) * w + b with plain gains (tensor <norm>) and biases (tensor <norm>.b)
+    shared_norm: bool = False  # parallel blocks: the mixer and the feed-forward read ONE normed row (norm1; there is no norm2)
+    loop_in: bool = False     # before the first layer of every pass of the loop: x <- W [x; x0] (tensor loop.in [W, 2 W], x0 the embedding output)
+    logit_softcap: float = 0.0  # > 0: logits <- cap * tanh(logits / cap)
 
     def schedule(self):
         """Layer index of every layer RUN: layers loop_start .. loop_stop-1 run loop_times times in a row (same weights, own cache / state)."""
         n = len(self.layers)
         return list(range(self.loop_start)) + list(range(self.loop_start, self.loop_stop)) * self.loop_times + list(range(self.loop_stop, n))
+
+    def pass_starts(self):
+        """Indices into schedule() of the runs that begin a pass of the loop."""
+        span = self.loop_stop - self.loop_start
+        return [self.loop_start + k * span for k in range(self.loop_times)] if span > 0 else []
 
 
 def _parse_rot(r: dict) -> RotaryConfig:
@@ -256,8 +296,49 @@ def parse_toderax(c: dict) -> HybridConfig:
                         embed_scale=float((c.get("embedding") or {}).get("scale", 1.0)))
 
 
+def parse_nusuvik(c: dict) -> HybridConfig:
+    """Nusuvik: parallel layers with ONE layer norm (gain and bias) that both the mixer and the feed-forward read; mixer `latent_attention`
+    (latent queries, a cached key/value latent with a shared rotated key part, a sigmoid gate per head); feed-forwards dense (gelu_tanh between
+    two biased projections) or a mixture of experts (sigmoid scores, a correction for the choice, groups of experts, silu-gated experts);
+    hashed pair embedding; a looped span of layers whose every pass starts with a projection of [stream; embedding output]; final layer norm
+    and a tanh cap on the logits."""
+    layers = []
+    for ly in c["layers"]:
+        m = ly["mixer"]
+        if ly["type"] == "latent_attention":
+            r = m.get("rot")
+            rot = RotaryConfig(int(r["dims"]), float(r["base"]), layout="half") if r else None
+            mixer = LatentAttentionMixerConfig(int(m["heads"]), int(m["dim"]), int(m["rot_dim"]), int(m["vdim"]), int(m["kv_rank"]), int(m["q_rank"]),
+                                               rot, float(m["scale"]))
+            if rot is not None and (rot.dims > mixer.rot_dim or rot.dims % 2):
+                raise ValueError("latent attention rotates an even number of at most rot_dim entries")
+        else:
+            raise ValueError(f"unknown mixer type {ly['type']!r}")
+        mlp = ly.get("mlp")
+        if mlp is None:
+            ff = None
+        elif mlp.get("kind") == "dense":
+            ff = MlpConfig("dense", int(mlp["ff"]), gated=False, bias=True)
+        elif mlp.get("kind") == "moe":
+            r = mlp["router"]
+            g = r.get("groups") or {}
+            ff = MoeConfig(int(r["experts"]), int(r["top"]), int(mlp["expert"]["ff"]), math.inf, alpha=1.0, up_shift=0.0, router="sigmoid",
+                           correction=True, groups=int(g.get("count", 1)), keep=int(g.get("keep", g.get("count", 1))))
+            if ff.experts % ff.groups or not 1 <= ff.keep <= ff.groups or not 1 <= ff.top <= ff.keep * (ff.experts // ff.groups):
+                raise ValueError("router: groups must divide the experts, 1 <= keep <= groups, top <= experts of the kept groups")
+        else:
+            raise ValueError(f"unknown feed-forward kind {mlp.get('kind')!r}")
+        layers.append(HybridLayerConfig(ly["type"], mixer, ff))
+    lp = c.get("loop") or {}
+    bg = (c.get("embedding") or {}).get("bigram") or {}
+    return HybridConfig("Nusuvik", int(c["vocab"]), int(c["width"]), float(c["norm"]["eps"]), tuple(layers),
+                        int(lp.get("start", 0)), int(lp.get("stop", 0)), int(lp.get("times", 1)),
+                        int(bg.get("buckets", 0)), int(bg.get("mul_prev", 0)), int(bg.get("mul_cur", 0)), norm_offset=0.0,
+                        norm_kind="layer", shared_norm=True, loop_in=bool(lp), logit_softcap=float(c.get("logit_softcap") or 0.0))
+
+
 # config.json "architecture" -> parser.  The quantised Llama-family models of MODELS are built by qserve_b200.decode.DecodeRunner.
-ARCHITECTURES: Dict[str, Callable[[dict], HybridConfig]] = {"Rizurax": parse_rizurax, "Toderax": parse_toderax}
+ARCHITECTURES: Dict[str, Callable[[dict], HybridConfig]] = {"Rizurax": parse_rizurax, "Toderax": parse_toderax, "Nusuvik": parse_nusuvik}
 
 
 def read_model_config(model_dir: str) -> HybridConfig:

@@ -873,11 +873,11 @@ def toderax_block(args):
                     "weights_frac_of_measured_hbm": 3 * W * (min(E, n * TOP) * moe.ff + moe.shared_ff) * 2 / tm / 1e9 / hbm_gbs}
             route, ti, tw = torch.empty(T, E, device=dev), torch.empty(T, TOP, dtype=torch.int32, device=dev), torch.empty(T, TOP, device=dev)
             tr = time_kernel(lambda: (check(lib.qs_hyb_moe_router(route.data_ptr(), ti.data_ptr(), tw.data_ptr(), h.data_ptr(), ly_g.ff.w_router.data_ptr(),
-                                                                  T, W, E, TOP, 0, raw())), 1)[1], reps, stream)
+                                                                  T, W, E, TOP, 0, None, 1, 1, 0, raw())), 1)[1], reps, stream)
             kern["moe_router"] = {"us": tr * 1e6, "frac_of_measured_hbm": T * W * 2 / tr / 1e9 / hbm_gbs}
             gu = torch.randn(T * TOP, 2 * moe.ff, device=dev).to(torch.bfloat16)
             act = torch.empty(T * TOP, moe.ff, dtype=torch.bfloat16, device=dev)
-            ta = time_kernel(lambda: (check(lib.qs_hyb_moe_act(act.data_ptr(), gu.data_ptr(), None, T * TOP, 0, 0, 0.0, moe.ff, 7.0, 1.702, 0, raw())), 1)[1],
+            ta = time_kernel(lambda: (check(lib.qs_hyb_moe_act(act.data_ptr(), gu.data_ptr(), None, T * TOP, 0, 0, 0.0, moe.ff, 7.0, 1.702, 1.0, 0, raw())), 1)[1],
                              reps, stream)
             kern["moe_clamped_activation"] = {"us": ta * 1e6, "frac_of_measured_hbm": T * TOP * moe.ff * 6 / ta / 1e9 / hbm_gbs}
             rec["kernels"] = kern

@@ -356,14 +356,18 @@ QS_API int qs_hyb_latent_query(void* qa, const void* qlat, const void* q, int64_
 QS_API int qs_hyb_latent_attention(void* out, const void* qa, const void* pool, const int32_t* tok_slot, const int32_t* tok_pos,
                                    const int32_t* block_table, int max_blocks, int tokens_n, int heads, int kv_rank, int rot_dim, float scale,
                                    int page_size, int chunk, int window, int dtype, void* stream);
-/* The same on the tensor cores (bfloat16 storage) where qs_hyb_latent_attention_fast_supported returns 1: the rows of a tile are (token, head)
- * pairs of one entry.  scratch: fp32, qs_hyb_latent_attention_scratch_floats elements. */
+/* The same on the tensor cores where qs_hyb_latent_attention_fast_supported returns 1 (bfloat16 storage, kv_rank in {32, 64, 128, 256, 512},
+ * kv_rank + rot_dim a multiple of 8): the 64 rows of a tile are (token, head) pairs of one sequence.  Entries of at least 16 tokens run by the
+ * tile tables of the batch (tile_entry / tile_row0: entry and first row of every span of 64 tokens), the tokens listed in short_tokens one
+ * by one with their cells shared out over several blocks.  scratch: fp32, qs_hyb_latent_attention_scratch_floats elements. */
 QS_API int qs_hyb_latent_attention_fast_supported(int dtype, int heads, int kv_rank, int rot_dim);
 QS_API int64_t qs_hyb_latent_attention_scratch_floats(int tokens, int heads, int kv_rank);
 QS_API int qs_hyb_latent_attention_fast(void* out, const void* qa, const void* pool, const int32_t* tok_slot, const int32_t* tok_pos,
-                                        const int32_t* block_table, int max_blocks, const int32_t* entry_start, const int32_t* entry_len,
-                                        const int32_t* entry_slot, const int32_t* entry_pos0, int entries, int tokens_n, float* scratch, int heads,
-                                        int kv_rank, int rot_dim, float scale, int page_size, int chunk, int window, int dtype, void* stream);
+                                        const int32_t* block_table, int max_blocks, const int32_t* tile_entry, const int32_t* tile_row0,
+                                        int n_tiles, const int32_t* short_tokens, int n_short, const int32_t* entry_start,
+                                        const int32_t* entry_len, const int32_t* entry_slot, const int32_t* entry_pos0, int tokens_n,
+                                        float* scratch, int heads, int kv_rank, int rot_dim, float scale, int page_size, int chunk, int window,
+                                        int dtype, void* stream);
 /* out[t, h * vdim + j] = ov[h, t, j] * sigmoid(gate[t, col_g + h]) (gate may be NULL: no gate); ov [heads, tokens, vdim] */
 QS_API int qs_hyb_latent_gate_out(void* out, int64_t out_stride, const void* ov, const void* gate, int64_t gate_stride, int col_g, int tokens_n,
                                   int heads, int vdim, int dtype, void* stream);

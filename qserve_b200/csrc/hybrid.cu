@@ -328,35 +328,6 @@ __global__ void __launch_bounds__(kAttnThreads) paged_multimap_attention_kernel(
 // ---------------------------------------------------------------------------------------------------------------------------------
 constexpr int kTileQ = 64, kTileK = 64, kPad = 8;
 
-__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
-}
-__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], const void* p) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
-}
-__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-  asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-// 2^x on the special-function unit (relative error about 2^-22; -inf gives 0): the bfloat16 kernels' softmax runs in the base-2 domain
-__device__ __forceinline__ float fast_exp2(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-// the leading bfloat16 terms of two fp32 numbers, packed; the numbers keep what is left
-__device__ __forceinline__ uint32_t split_bf16x2(float& lo, float& hi) {
-  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-  const uint32_t u = *reinterpret_cast<uint32_t*>(&v);
-  lo -= __uint_as_float(u << 16);
-  hi -= __uint_as_float(u & 0xffff0000u);
-  return u;
-}
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-  return *reinterpret_cast<uint32_t*>(&v);
-}
-
 template <int NVT, int PSPLIT, int KT>  // NVT = Dv / 16, KT keys per tile (64, or 32: less shared memory and fewer registers, 3 blocks per SM)
 __global__ void __launch_bounds__(128, KT == 32 ? 3 : 2) tile_attention_kernel(
     float* __restrict__ a_out, const __nv_bfloat16* __restrict__ q, long long q_stride, const __nv_bfloat16* __restrict__ kpool,

@@ -227,6 +227,289 @@ int launch_latent_attention(void* out, const void* qa, const void* pool, const i
   return check_cuda(cudaGetLastError(), "hyb_latent_attention");
 }
 
+// ---------------------------------------------------------------------------------------------------------------------------------
+// Latent attention on the tensor cores (bfloat16 storage).  The 64 rows of a tile are (token, head) pairs of ONE sequence: RT = 64 / HB
+// consecutive tokens x HB heads (row r: token r / HB, head r % HB).  All rows score the same cells, so a tile of 32 cells, streamed through
+// the block table with cp.async into a double buffer, meets 64 queries; the cells' first K columns are also the values (no second copy).
+// 8 warps: warp (rb, ch) owns rows [16 rb, 16 rb + 16) and the value columns [ch K/2, (ch + 1) K/2).  Both warps of a row block form the
+// same scores S = Q C^T (mma.sync m16n8k16, bf16 operands, fp32 accumulation) and the same online softmax (base 2, fp32), so no exchange
+// is needed; P V takes the fp32 weights as three bfloat16 terms (p = hi + mid + lo), i.e. at fp32 precision.
+// LONG: blocks walk the tiles of entries of at least 16 tokens (tile_entry / tile_row0 name 64-token spans; a block takes RT tokens of one)
+//       and write out [H][T][K] (bfloat16) directly.
+// SHORT: one listed token per block row, the cells shared out over `splits` blocks (blockIdx.z); un-normalised partial sums, running
+//       maximum and denominator go to `part` [n_short][H][splits][2 + K] fp32, latent_merge_kernel finishes.
+// ---------------------------------------------------------------------------------------------------------------------------------
+constexpr int kLtRows = 64, kLtKT = 32, kLtPad = 8, kLtTokensPerSpan = 64;
+
+template <int NVT, bool SHORT>  // K = 32 NVT: NVT value column blocks of 16 per warp
+__global__ void __launch_bounds__(256, 1) latent_tile_kernel(
+    __nv_bfloat16* __restrict__ out, float* __restrict__ part, const __nv_bfloat16* __restrict__ qa, const __nv_bfloat16* __restrict__ pool,
+    const int* __restrict__ tile_entry, const int* __restrict__ tile_row0, const int* __restrict__ short_tokens, const int* __restrict__ tok_slot,
+    const int* __restrict__ tok_pos, const int* __restrict__ entry_start, const int* __restrict__ entry_len, const int* __restrict__ entry_slot,
+    const int* __restrict__ entry_pos0, const int* __restrict__ block_table, int max_blocks, int T, int H, int HB, int R, float scale, int page,
+    int chunk, int window, int splits) {
+  extern __shared__ __align__(16) unsigned char smraw[];
+  constexpr int K = 32 * NVT;
+  const int DK = K + R, DKP = (DK + 15) & ~15, SD = DKP + kLtPad;
+  __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smraw);  // [64][SD]
+  __nv_bfloat16* Ks = Qs + kLtRows * SD;                        // [2][32][SD]
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, rb = warp & 3, ch = warp >> 2;
+  const int RT = kLtRows / HB, h0 = blockIdx.y * HB;
+  int tok0, n_tok, pos0, slot;
+  if (SHORT) {
+    tok0 = short_tokens[blockIdx.x];
+    n_tok = 1;
+    pos0 = tok_pos[tok0];
+    slot = tok_slot[tok0];
+  } else {
+    const int per_span = kLtTokensPerSpan / RT;
+    const int tile = blockIdx.x / per_span, sub = blockIdx.x - tile * per_span;
+    const int e = tile_entry[tile], r0 = tile_row0[tile] + sub * RT;
+    n_tok = min(RT, entry_len[e] - r0);
+    if (n_tok <= 0) return;
+    tok0 = entry_start[e] + r0;
+    pos0 = entry_pos0[e] + r0;
+    slot = entry_slot[e];
+  }
+  const int* bt = block_table + (size_t)slot * max_blocks;
+  // queries: 16-byte chunks, zero rows for (token, head) pairs that do not exist, zero columns up to a multiple of 16
+  const int dch = DK >> 3, sch = DKP >> 3;
+  for (int c = tid; c < kLtRows * sch; c += 256) {
+    const int r = c / sch, cc = c - r * sch;
+    const int tk = r / HB, hh = h0 + r % HB;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (tk < n_tok && hh < H && cc < dch) v = *reinterpret_cast<const uint4*>(qa + ((size_t)(tok0 + tk) * H + hh) * DK + cc * 8);
+    *reinterpret_cast<uint4*>(Qs + r * SD + cc * 8) = v;
+  }
+  const int last_pos = pos0 + n_tok - 1;
+  int kt_lo = first_key(pos0, chunk, window) / kLtKT, kt_hi = last_pos / kLtKT + 1;  // tiles [kt_lo, kt_hi)
+  if (SHORT) {
+    const int per = (kt_hi - kt_lo + splits - 1) / splits;
+    kt_lo += blockIdx.z * per;
+    kt_hi = min(kt_hi, kt_lo + per);
+  }
+  const bool live = rb * 16 < n_tok * HB;  // a row block without any real (token, head) pair only helps to load
+  const int qrow = rb * 16 + (lane >> 2);  // this thread's rows: qrow, qrow + 8
+  const int qp[2] = {pos0 + min(qrow / HB, n_tok - 1), pos0 + min((qrow + 8) / HB, n_tok - 1)};
+  const int fk[2] = {first_key(qp[0], chunk, window), first_key(qp[1], chunk, window)};
+  const int warp_qp_min = pos0 + min(rb * 16 / HB, n_tok - 1);
+  const float scale_log2 = scale * 1.4426950408889634f;
+  float o[2 * NVT][4];
+#pragma unroll
+  for (int i = 0; i < 2 * NVT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  // 8 threads per cell row, alternating 16-byte chunks; the block-table lookup is made one tile ahead of its use
+  auto cell_of = [&](int kt) -> long long {
+    const int kp = kt * kLtKT + (tid >> 3);
+    return kp <= last_pos ? (long long)bt[kp / page] * page + kp % page : -1;
+  };
+  auto load_tile = [&](int buf, long long cell) {
+    __nv_bfloat16* Kd = Ks + ((size_t)buf * kLtKT + (tid >> 3)) * SD;
+    if (cell >= 0) {
+      const __nv_bfloat16* src = pool + (size_t)cell * DK;
+      for (int cc = tid & 7; cc < sch; cc += 8) {
+        if (cc < dch) cp_async16(Kd + cc * 8, src + cc * 8);
+        else *reinterpret_cast<uint4*>(Kd + cc * 8) = make_uint4(0, 0, 0, 0);
+      }
+    } else {
+      for (int cc = tid & 7; cc < sch; cc += 8) *reinterpret_cast<uint4*>(Kd + cc * 8) = make_uint4(0, 0, 0, 0);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  if (kt_lo < kt_hi) load_tile(kt_lo & 1, cell_of(kt_lo));
+  long long cell_next = kt_lo + 1 < kt_hi ? cell_of(kt_lo + 1) : -1;
+  for (int kt = kt_lo; kt < kt_hi; ++kt) {
+    if (kt + 1 < kt_hi) {
+      load_tile((kt + 1) & 1, cell_next);
+      if (kt + 2 < kt_hi) cell_next = cell_of(kt + 2);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    __syncthreads();
+    if (live) {
+      const __nv_bfloat16* Kc = Ks + (size_t)(kt & 1) * kLtKT * SD;
+      float s[kLtKT / 8][4];
+#pragma unroll
+      for (int i = 0; i < kLtKT / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+      for (int ks = 0; ks < DKP; ks += 16) {
+        uint32_t a[4];
+        ldsm_x4(a, Qs + (rb * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * SD + ks + (lane >> 4) * 8);
+#pragma unroll
+        for (int np = 0; np < kLtKT / 16; ++np) {
+          uint32_t b[4];
+          ldsm_x4(b, Kc + (np * 16 + (lane & 7) + (lane >> 4) * 8) * SD + ks + ((lane >> 3) & 1) * 8);
+          mma_bf16(s[2 * np], a, b[0], b[1]);
+          mma_bf16(s[2 * np + 1], a, b[2], b[3]);
+        }
+      }
+      // scale, mask (rows of one warp belong to different tokens: each has its own last and first visible cell), online softmax
+      float mx[2] = {-INFINITY, -INFINITY};
+      const bool edge = kt * kLtKT + kLtKT - 1 > warp_qp_min || chunk > 0 || window > 0;
+#pragma unroll
+      for (int nt = 0; nt < kLtKT / 8; ++nt)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float v = s[nt][j] * scale_log2;
+          if (edge) {
+            const int kpos = kt * kLtKT + nt * 8 + (lane & 3) * 2 + (j & 1);
+            if (kpos > qp[j >> 1] || kpos < fk[j >> 1]) v = -INFINITY;
+          }
+          s[nt][j] = v;
+          mx[j >> 1] = fmaxf(mx[j >> 1], v);
+        }
+      float corr[2];
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+        const float m_new = fmaxf(m_run[r], mx[r]);
+        corr[r] = m_new == -INFINITY ? 1.f : fast_exp2(m_run[r] - m_new);
+        m_run[r] = m_new;
+        l_run[r] *= corr[r];
+      }
+#pragma unroll
+      for (int nt = 0; nt < kLtKT / 8; ++nt)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float mm = m_run[j >> 1];
+          const float p = mm == -INFINITY ? 0.f : fast_exp2(s[nt][j] - mm);
+          s[nt][j] = p;
+          l_run[j >> 1] += p;
+        }
+#pragma unroll
+      for (int i = 0; i < 2 * NVT; ++i) {
+        o[i][0] *= corr[0]; o[i][1] *= corr[0]; o[i][2] *= corr[1]; o[i][3] *= corr[1];
+      }
+      constexpr int NVG = NVT % 4 == 0 ? 4 : (NVT % 2 == 0 ? 2 : 1);
+      const __nv_bfloat16* Vc = Kc + ch * (K / 2);  // the values: this warp's half of the cells' first K columns
+#pragma unroll
+      for (int kk = 0; kk < kLtKT / 16; ++kk) {
+        uint32_t a[3][4];
+#pragma unroll
+        for (int pt = 0; pt < 4; ++pt) {
+          const int nt = 2 * kk + (pt >> 1), j0 = (pt & 1) * 2;
+          float r0v = s[nt][j0], r1v = s[nt][j0 + 1];
+#pragma unroll
+          for (int sp = 0; sp < 3; ++sp) a[sp][pt] = split_bf16x2(r0v, r1v);
+        }
+#pragma unroll
+        for (int nv0 = 0; nv0 < NVT; nv0 += NVG) {
+          uint32_t b[NVG][4];
+#pragma unroll
+          for (int i = 0; i < NVG; ++i)
+            ldsm_x4_trans(b[i], Vc + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * SD + (nv0 + i) * 16 + (lane >> 4) * 8);
+#pragma unroll
+          for (int sp = 0; sp < 3; ++sp)
+#pragma unroll
+            for (int i = 0; i < NVG; ++i) {
+              mma_bf16(o[2 * (nv0 + i)], a[sp], b[i][0], b[i][1]);
+              mma_bf16(o[2 * (nv0 + i) + 1], a[sp], b[i][2], b[i][3]);
+            }
+        }
+      }
+    }
+    __syncthreads();  // every warp is done with this buffer before tile kt + 2 streams into it
+  }
+  if (!live) return;
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+  }
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int row = qrow + r * 8, tk = row / HB, hh = h0 + row % HB;
+    if (tk >= n_tok || hh >= H) continue;
+    const int col0 = ch * (K / 2) + (lane & 3) * 2;
+    if (SHORT) {
+      float* dst = part + (((size_t)blockIdx.x * H + hh) * splits + blockIdx.z) * (size_t)(2 + K);
+      if (ch == 0 && (lane & 3) == 0) {
+        dst[0] = m_run[r];
+        dst[1] = l_run[r];
+      }
+#pragma unroll
+      for (int i = 0; i < 2 * NVT; ++i) *reinterpret_cast<float2*>(dst + 2 + col0 + i * 8) = make_float2(o[i][2 * r], o[i][2 * r + 1]);
+    } else {
+      const float inv = 1.f / l_run[r];
+      __nv_bfloat16* dst = out + ((size_t)hh * T + tok0 + tk) * (size_t)K + col0;
+#pragma unroll
+      for (int i = 0; i < 2 * NVT; ++i) *reinterpret_cast<uint32_t*>(dst + i * 8) = pack_bf16(o[i][2 * r] * inv, o[i][2 * r + 1] * inv);
+    }
+  }
+}
+
+// out[h][t][:] = sum_z 2^(m_z - M) o_z / sum_z 2^(m_z - M) l_z over the key shares of a listed token.  One warp per (listed token, head).
+__global__ void latent_merge_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict__ part, const int* __restrict__ short_tokens, int n_short,
+                                    int T, int H, int K, int splits) {
+  const int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (w >= n_short * H) return;
+  const int i = w / H, h = w - i * H;
+  const float* p = part + (size_t)w * splits * (2 + K);
+  float M = -INFINITY;
+  for (int z = 0; z < splits; ++z) M = fmaxf(M, p[(size_t)z * (2 + K)]);
+  float L = 0.f;
+  for (int z = 0; z < splits; ++z) {
+    const float m = p[(size_t)z * (2 + K)];
+    if (m != -INFINITY) L += fast_exp2(m - M) * p[(size_t)z * (2 + K) + 1];
+  }
+  const float inv = 1.f / L;
+  __nv_bfloat16* dst = out + ((size_t)h * T + short_tokens[i]) * (size_t)K;
+  for (int c = lane; c < K; c += 32) {
+    float a = 0.f;
+    for (int z = 0; z < splits; ++z) {
+      const float m = p[(size_t)z * (2 + K)];
+      if (m != -INFINITY) a += fast_exp2(m - M) * p[(size_t)z * (2 + K) + 2 + c];
+    }
+    dst[c] = __float2bfloat16_rn(a * inv);
+  }
+}
+
+constexpr int kLtTargetBlocks = 296;  // key shares of single tokens are chosen to give about two blocks per SM
+constexpr int kLtMaxSplits = 16;
+
+bool latent_fast_supported(int dtype, int heads, int kv_rank, int rot_dim) {
+  if (dtype != QS_DTYPE_BF16 || heads < 1 || rot_dim < 0) return false;
+  if (!(kv_rank == 32 || kv_rank == 64 || kv_rank == 128 || kv_rank == 256 || kv_rank == 512)) return false;
+  const int dkp = (kv_rank + rot_dim + 15) & ~15;
+  return (kv_rank + rot_dim) % 8 == 0 && (size_t)(kLtRows + 2 * kLtKT) * (dkp + kLtPad) * 2 <= 200 * 1024;
+}
+
+int latent_head_block(int heads) { return heads <= 16 ? 16 : (heads <= 32 ? 32 : 64); }
+
+int latent_splits(int n_short, int heads) {
+  const int groups = (heads + latent_head_block(heads) - 1) / latent_head_block(heads);
+  return std::max(1, std::min(kLtMaxSplits, kLtTargetBlocks / std::max(1, n_short * groups)));
+}
+
+template <int NVT>
+int launch_latent_tiles(void* out, float* part, const void* qa, const void* pool, const int* tile_entry, const int* tile_row0, int n_tiles,
+                        const int* short_tokens, int n_short, const int* tok_slot, const int* tok_pos, const int* entry_start, const int* entry_len,
+                        const int* entry_slot, const int* entry_pos0, const int* block_table, int max_blocks, int T, int H, int R, float scale,
+                        int page, int chunk, int window, cudaStream_t s) {
+  const int K = 32 * NVT, HB = latent_head_block(H), groups = (H + HB - 1) / HB, dkp = (K + R + 15) & ~15;
+  const size_t smem = (size_t)(kLtRows + 2 * kLtKT) * (dkp + kLtPad) * sizeof(__nv_bfloat16);
+  static bool attr_set[kMaxDevices] = {};
+  if (!attr_set[device_ordinal()]) {
+    if (int rc = check_cuda(cudaFuncSetAttribute(latent_tile_kernel<NVT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024), "latent tiles smem")) return rc;
+    if (int rc = check_cuda(cudaFuncSetAttribute(latent_tile_kernel<NVT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024), "latent tiles smem")) return rc;
+    attr_set[device_ordinal()] = true;
+  }
+  if (n_tiles > 0)
+    latent_tile_kernel<NVT, false><<<dim3(n_tiles * (kLtTokensPerSpan / (kLtRows / HB)), groups), 256, smem, s>>>(
+        (__nv_bfloat16*)out, nullptr, (const __nv_bfloat16*)qa, (const __nv_bfloat16*)pool, tile_entry, tile_row0, nullptr, tok_slot, tok_pos, entry_start,
+        entry_len, entry_slot, entry_pos0, block_table, max_blocks, T, H, HB, R, scale, page, chunk, window, 1);
+  if (n_short > 0) {
+    const int splits = latent_splits(n_short, H);
+    latent_tile_kernel<NVT, true><<<dim3(n_short, groups, splits), 256, smem, s>>>(
+        (__nv_bfloat16*)out, part, (const __nv_bfloat16*)qa, (const __nv_bfloat16*)pool, nullptr, nullptr, short_tokens, tok_slot, tok_pos, entry_start,
+        entry_len, entry_slot, entry_pos0, block_table, max_blocks, T, H, HB, R, scale, page, chunk, window, splits);
+    const int warps = n_short * H;
+    latent_merge_kernel<<<(warps + 3) / 4, 128, 0, s>>>((__nv_bfloat16*)out, part, short_tokens, n_short, T, H, K, splits);
+  }
+  return check_cuda(cudaGetLastError(), "hyb_latent_attention_fast");
+}
+
 // out[t][h * Dv + j] = ov[h][t][j] * sigmoid(gate[t][col_g + h])   (gate == null: no gate).  One block per token.
 template <typename ST>
 __global__ void latent_gate_out_kernel(ST* __restrict__ out, long long out_stride, const ST* __restrict__ ov, const ST* __restrict__ gate,
@@ -310,15 +593,37 @@ int qs_hyb_latent_attention(void* out, const void* qa, const void* pool, const i
   return qs::QS_OK;
 }
 
-int qs_hyb_latent_attention_fast_supported(int dtype, int heads, int kv_rank, int rot_dim) { return 0; }
+int qs_hyb_latent_attention_fast_supported(int dtype, int heads, int kv_rank, int rot_dim) {
+  return latent_fast_supported(dtype, heads, kv_rank, rot_dim) ? 1 : 0;
+}
 
-int64_t qs_hyb_latent_attention_scratch_floats(int tokens, int heads, int kv_rank) { return 0; }
+int64_t qs_hyb_latent_attention_scratch_floats(int tokens, int heads, int kv_rank) {
+  // the key shares of single tokens: [tokens x shares][heads][2 + kv_rank]; tokens x shares never exceeds tokens + the target block count
+  return ((int64_t)tokens + kLtTargetBlocks) * heads * (2 + kv_rank);
+}
 
 int qs_hyb_latent_attention_fast(void* out, const void* qa, const void* pool, const int32_t* tok_slot, const int32_t* tok_pos, const int32_t* block_table,
-                                 int max_blocks, const int32_t* entry_start, const int32_t* entry_len, const int32_t* entry_slot,
-                                 const int32_t* entry_pos0, int entries, int tokens_n, float* scratch, int heads, int kv_rank, int rot_dim, float scale,
+                                 int max_blocks, const int32_t* tile_entry, const int32_t* tile_row0, int n_tiles, const int32_t* short_tokens,
+                                 int n_short, const int32_t* entry_start, const int32_t* entry_len, const int32_t* entry_slot,
+                                 const int32_t* entry_pos0, int tokens_n, float* scratch, int heads, int kv_rank, int rot_dim, float scale,
                                  int page_size, int chunk, int window, int dtype, void* stream) {
-  return set_error(qs::QS_ERR_INVALID, "hyb_latent_attention_fast: shape not supported (use qs_hyb_latent_attention)");
+  QS_REQUIRE(out && qa && pool && tok_slot && tok_pos && block_table, "hyb_latent_attention_fast: null tensor");
+  QS_REQUIRE(latent_fast_supported(dtype, heads, kv_rank, rot_dim), "hyb_latent_attention_fast: shape not supported (use qs_hyb_latent_attention)");
+  QS_REQUIRE(chunk >= 0 && window >= 0 && page_size > 0, "hyb_latent_attention_fast: bad mask or page size");
+  QS_REQUIRE(n_tiles == 0 || (tile_entry && tile_row0 && entry_start && entry_len && entry_slot && entry_pos0), "hyb_latent_attention_fast: null tile table");
+  QS_REQUIRE(n_short == 0 || (short_tokens && scratch), "hyb_latent_attention_fast: null token list");
+  cudaStream_t s = (cudaStream_t)stream;
+#define QS_LT(NVT)                                                                                                                              \
+  return launch_latent_tiles<NVT>(out, scratch, qa, pool, tile_entry, tile_row0, n_tiles, short_tokens, n_short, tok_slot, tok_pos, entry_start, \
+                                  entry_len, entry_slot, entry_pos0, block_table, max_blocks, tokens_n, heads, rot_dim, scale, page_size, chunk, window, s)
+  switch (kv_rank / 32) {
+    case 1: QS_LT(1);
+    case 2: QS_LT(2);
+    case 4: QS_LT(4);
+    case 8: QS_LT(8);
+    default: QS_LT(16);
+  }
+#undef QS_LT
 }
 
 int qs_hyb_latent_gate_out(void* out, int64_t out_stride, const void* ov, const void* gate, int64_t gate_stride, int col_g, int tokens_n, int heads,

@@ -364,8 +364,9 @@ class LatentAttentionMixer(_Mixer):
         olat = torch.empty((H, T, K), dtype=proj.dtype, device=dev)
         if scratch is not None and LATENT_IMPL != "plain" and lib.qs_hyb_latent_attention_fast_supported(dt, H, K, R) == 1:
             check(lib.qs_hyb_latent_attention_fast(olat.data_ptr(), qa.data_ptr(), pool.data_ptr(), _p(b.tok_slot), _p(b.tok_pos), _p(b.block_table),
-                                                   b.block_table.shape[1], _p(b.entry_start), _p(b.entry_len), _p(b.entry_slot), _p(b.entry_pos0),
-                                                   b.n_entries, T, scratch.data_ptr(), H, K, R, m.scale, page_size, m.chunk, m.window, dt, stream))
+                                                   b.block_table.shape[1], _p(b.tile_entry), _p(b.tile_row0), b.n_tiles, _p(b.short_tokens), b.n_short,
+                                                   _p(b.entry_start), _p(b.entry_len), _p(b.entry_slot), _p(b.entry_pos0), T, scratch.data_ptr(), H, K,
+                                                   R, m.scale, page_size, m.chunk, m.window, dt, stream))
         else:
             check(lib.qs_hyb_latent_attention(olat.data_ptr(), qa.data_ptr(), pool.data_ptr(), _p(b.tok_slot), _p(b.tok_pos), _p(b.block_table),
                                               b.block_table.shape[1], T, H, K, R, m.scale, page_size, m.chunk, m.window, dt, stream))

@@ -90,8 +90,8 @@ def test_router_kernel(dev, experts, top, width, T):
     h, wr = torch.randn(T, width, generator=g), torch.randn(experts, width, generator=g) * width ** -0.5
     hd, wd = h.to(dev), wr.to(dev)
     route, idx, wt = torch.zeros(T, experts, device=dev), torch.zeros(T, top, dtype=torch.int32, device=dev), torch.zeros(T, top, device=dev)
-    check(lib.qs_hyb_moe_router(route.data_ptr(), idx.data_ptr(), wt.data_ptr(), hd.data_ptr(), wd.data_ptr(), T, width, experts, top, 1,
-                                torch.cuda.current_stream().cuda_stream))
+    check(lib.qs_hyb_moe_router(route.data_ptr(), idx.data_ptr(), wt.data_ptr(), hd.data_ptr(), wd.data_ptr(), T, width, experts, top, 0,
+                                None, 1, 1, 1, torch.cuda.current_stream().cuda_stream))
     score = torch.softmax(h.double() @ wr.double().T, -1)
     best = torch.topk(score, top, -1)
     assert torch.equal(idx.cpu().long(), best.indices)

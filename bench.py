@@ -17,6 +17,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
 import subprocess
 import sys
@@ -60,6 +61,10 @@ def parse():
     ap.add_argument("--toderax", action="store_true", help="instead of the default workload: prefill and decode throughput of the Toderax decoder "
                     "(hyper-connection streams, gate recurrence, chunked sink attention beside retention, mixture of experts; random weights) at "
                     "layer sizes of real models, beside the Rizurax hybrid decoder at equal size; prints one JSON line")
+    ap.add_argument("--nusuvik", action="store_true", help="instead of the default workload: prefill and decode throughput of the Nusuvik decoder "
+                    "(latent attention over a cache of latent rows, one layer norm per parallel block, dense and grouped-sigmoid expert "
+                    "feed-forwards, loop input projection; random weights) at layer sizes of real models, beside the Rizurax hybrid decoder at "
+                    "equal size; prints one JSON line")
     return ap.parse_args()
 
 
@@ -937,6 +942,189 @@ def toderax_block(args):
 
 
 # ------------------------------------------------------------------------------------------------------------
+# --nusuvik: the Nusuvik decoder beside the closest existing model (the Rizurax hybrid decoder) at equal size
+# ------------------------------------------------------------------------------------------------------------
+def nusuvik_block(args):
+    """Prefill (4 prompts x 2048 tokens in one step) and decode (64 sequences at 1024 tokens of context) of a four-layer stack of latent
+    attention layers (key/value latent 512 + 64 rotated numbers per position, query latent 3/4 of the width, head size 128 + 64 rotated,
+    value size 128) with feed-forwards dense | experts | dense | experts (32 experts in 4 groups of which 2 are kept, 8 per token, expert
+    size = feed-forward / 8), the first two layers a loop that runs twice.  Whole steps are captured in CUDA graphs (device time); the
+    design's kernels are timed one by one with their algorithmic bytes / flops against the measured copy and bf16 GEMM peaks.  Beside it:
+    the Rizurax stack (attention | delta | attention | delta, dense feed-forward) at equal width / heads / head size, the kernels that play
+    the same parts there, and the softmax-routed expert mixture of the Toderax design at equal expert sizes."""
+    import torch
+
+    from qserve_b200._lib import check, lib
+    from qserve_b200.engine import Engine
+    from qserve_b200.hybrid import FEED_FORWARDS, HybridDecoder, StepBatch, random_weights
+    from qserve_b200.modelcfg import (AttentionMixerConfig, DeltaMixerConfig, HybridConfig, HybridLayerConfig, LatentAttentionMixerConfig, MlpConfig,
+                                      MoeConfig, RotaryConfig)
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    hbm_gbs = peaks()[0]
+    try:
+        tflops = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops"]
+    except (OSError, KeyError, ValueError):
+        tflops = 1590.0
+    stream = torch.cuda.current_stream()
+    reps = max(3, args.kernel_reps)
+    raw = lambda: torch._C._cuda_getCurrentRawStream(0)
+    B, CTX, NP, LP, E, TOP, KR, R = 64, 1024, 4, 2048, 32, 8, 512, 64
+    out = {"metric": "Nusuvik decoder throughput (tokens/s, random weights, bf16, 4 layers of which 2 run twice)", "unit": "tokens/s", "impl": "ours",
+           "dtype": "bf16", "data": "synthetic", "peaks": {"hbm_gbs": hbm_gbs, "bf16_tflops": tflops}, "sizes": {}}
+
+    def steps(model, eng, V, g):
+        prompts = [torch.randint(0, V, (LP,), generator=g).tolist() for _ in range(NP)]
+        for i, p_ in enumerate(prompts):
+            eng.cache.admit(("p", i)); eng.cache.reserve(("p", i), LP)
+        pb = StepBatch.build([(eng.cache.seqs[("p", i)].slot, 0, -1, p_) for i, p_ in enumerate(prompts)], eng.cache.sync_block_table(), dev)
+        t = time_kernel(lambda: (model.forward(pb, eng.cache), 1)[1], reps, stream)
+        rec = {"prefill": {"tokens": NP * LP, "ms": t * 1e3, "tokens_per_s": NP * LP / t}}
+        for i in range(B):
+            eng.cache.admit(("d", i)); eng.cache.reserve(("d", i), CTX + 1)
+        db = StepBatch.build([(eng.cache.seqs[("d", i)].slot, CTX, 5, [int(torch.randint(0, V, (1,), generator=g))]) for i in range(B)],
+                             eng.cache.sync_block_table(), dev)
+        t = time_kernel(lambda: (model.logits(model.forward(db, eng.cache)), 1)[1], reps * 4, stream)
+        rec["decode"] = {"batch": B, "ctx": CTX, "ms": t * 1e3, "tokens_per_s": B / t}
+        return rec, pb, db
+
+    def mixer_times(mixer, run_cache, pb, db, T):
+        proj = torch.randn(T, mixer.in_features, device=dev).to(torch.bfloat16)
+        cat = torch.empty(T, mixer.out_features, dtype=torch.bfloat16, device=dev)
+        scratch = torch.empty(max(1, mixer.scratch_floats(T)), dtype=torch.float32, device=dev)
+        tp = time_kernel(lambda: (mixer.run(proj, cat, pb, run_cache, 64, scratch, 0, raw()), 1)[1], reps, stream)
+        td = time_kernel(lambda: (mixer.run(proj[:B], cat[:B], db, run_cache, 64, scratch, 0, raw()), 1)[1], reps * 4, stream)
+        return tp, td
+
+    def ff_times(ff, h, label_fn, kern, useful_flops, weight_bytes):
+        for label, hh, r_ in (("prefill", h, reps), ("decode", h[:B].contiguous(), reps * 4)):
+            tm = time_kernel(lambda: (ff.run(hh, 0, raw()), 1)[1], r_, stream)
+            n = hh.shape[0]
+            kern[label_fn(label)] = {"us": tm * 1e6, "tflops": n * useful_flops / tm / 1e12, "frac_of_measured_bf16_peak": n * useful_flops / tm / 1e12 / tflops,
+                                     "weights_frac_of_measured_hbm": weight_bytes(n) / tm / 1e9 / hbm_gbs}
+
+    for name, (W, H, G, D, FF, V) in HYBRID_SIZES.items():
+        T, pairs = NP * LP, NP * (LP * (LP + 1) // 2)
+        lat = LatentAttentionMixerConfig(H, D, R, D, KR, 3 * W // 4, RotaryConfig(R, 1e6, layout="half"), (D + R) ** -0.5)
+        moe = MoeConfig(E, TOP, FF // TOP, math.inf, alpha=1.0, up_shift=0.0, router="sigmoid", correction=True, groups=4, keep=2)
+        dense = MlpConfig("dense", FF, gated=False, bias=True)
+        cfg = HybridConfig("Nusuvik", V, W, 1e-5, tuple(HybridLayerConfig("latent_attention", lat, f) for f in (dense, moe, dense, moe)),
+                           0, 2, 2, 4093, 131, 11, norm_offset=0.0, norm_kind="layer", shared_norm=True, loop_in=True, logit_softcap=30.0)
+        g = torch.Generator().manual_seed(0)
+        with torch.no_grad():
+            model = HybridDecoder(cfg, random_weights(cfg, 0, dev), torch.bfloat16, dev)
+            eng = Engine(model, max_tokens=B * (CTX + 64) + NP * LP, max_seqs=B + NP)
+            rec, pb, db = steps(model, eng, V, g)
+            kern = {}
+            mx = model.layers[0].mixer
+            tp, td = mixer_times(mx, eng.cache.runs[0], pb, db, T)
+            # useful work: scores and weighted values of heads of size (D + R) and D; executed: the same over the latent's K + R and K numbers
+            useful, executed = H * pairs * 2 * (D + R + D), H * pairs * 2 * (KR + R + KR)
+            kern["latent_attention_prefill(norms+append+q up+key up+rotate+attention+value up+gate)"] = {
+                "us": tp * 1e6, "useful_tflops": useful / tp / 1e12, "executed_tflops": executed / tp / 1e12,
+                "frac_of_measured_bf16_peak_useful": useful / tp / 1e12 / tflops, "frac_of_measured_bf16_peak_executed": executed / tp / 1e12 / tflops}
+            kern["latent_attention_decode(the same)"] = {"us": td * 1e6, "frac_of_measured_hbm": B * (CTX + 1) * (KR + R) * 2 / td / 1e9 / hbm_gbs}
+            # the attention kernels alone
+            qa = torch.randn(T, H, KR + R, device=dev).to(torch.bfloat16)
+            ol = torch.empty(H, T, KR, dtype=torch.bfloat16, device=dev)
+            scratch = torch.empty(max(1, mx.scratch_floats(T)), dtype=torch.float32, device=dev)
+            pool = eng.cache.runs[0]["c"]
+
+            def attn(b_, n):
+                check(lib.qs_hyb_latent_attention_fast(ol.data_ptr(), qa.data_ptr(), pool.data_ptr(), b_.tok_slot.data_ptr(), b_.tok_pos.data_ptr(),
+                                                       b_.block_table.data_ptr(), b_.block_table.shape[1], b_.tile_entry.data_ptr(), b_.tile_row0.data_ptr(),
+                                                       b_.n_tiles, b_.short_tokens.data_ptr(), b_.n_short, b_.entry_start.data_ptr(), b_.entry_len.data_ptr(),
+                                                       b_.entry_slot.data_ptr(), b_.entry_pos0.data_ptr(), n, scratch.data_ptr(), H, KR, R, lat.scale, 64, 0, 0,
+                                                       0, raw()))
+                return 1
+            ta = time_kernel(lambda: attn(pb, T), reps, stream)
+            kern["latent_tile_kernel_prefill"] = {"us": ta * 1e6, "useful_tflops": useful / ta / 1e12, "executed_tflops": executed / ta / 1e12,
+                                                  "frac_of_measured_bf16_peak_useful": useful / ta / 1e12 / tflops,
+                                                  "frac_of_measured_bf16_peak_executed": executed / ta / 1e12 / tflops}
+            ta = time_kernel(lambda: attn(db, B), reps * 4, stream)
+            kern["latent_tile_kernel_decode(+merge)"] = {"us": ta * 1e6, "frac_of_measured_hbm": B * (CTX + 1) * (KR + R) * 2 / ta / 1e9 / hbm_gbs}
+            # the same kernel on 8 times the context, over a pool of its own: a step's cells (600 MB) exceed L2 several times over
+            LONG = 8 * CTX
+            big = torch.randn(B * LONG // 64, 64, KR + R, device=dev).to(torch.bfloat16)
+            lt = torch.arange(B * LONG // 64, dtype=torch.int32, device=dev).view(B, LONG // 64).contiguous()
+            lb = StepBatch.build([(i, LONG - 1, 5, [1]) for i in range(B)], lt, dev)
+
+            def attn_long():
+                check(lib.qs_hyb_latent_attention_fast(ol.data_ptr(), qa.data_ptr(), big.data_ptr(), lb.tok_slot.data_ptr(), lb.tok_pos.data_ptr(),
+                                                       lt.data_ptr(), lt.shape[1], None, None, 0, lb.short_tokens.data_ptr(), lb.n_short, None, None, None,
+                                                       None, B, scratch.data_ptr(), H, KR, R, lat.scale, 64, 0, 0, 0, raw()))
+                return 1
+            ta = time_kernel(attn_long, reps * 2, stream)
+            kern[f"latent_tile_kernel_decode(+merge), context {LONG}"] = {"us": ta * 1e6, "frac_of_measured_hbm": B * LONG * (KR + R) * 2 / ta / 1e9 / hbm_gbs}
+            del big, lt, lb
+            del qa, ol
+            ly = model.layers[0]
+            x = torch.randn(T, W, device=dev)
+            h1, upd = torch.empty(T, W, dtype=torch.bfloat16, device=dev), torch.zeros(T, W, dtype=torch.bfloat16, device=dev)
+            tn = time_kernel(lambda: (check(lib.qs_hyb_stream_update_norm(h1.data_ptr(), None, x.data_ptr(), None, upd.data_ptr(), 0, None, 0,
+                                                                          ly.out_bias.data_ptr(), ly.norm1.data_ptr(), ly.norm1_b.data_ptr(), 2, 1e-5, T, W,
+                                                                          0, raw())), 1)[1], reps, stream)
+            kern["add_bias_layer_norm"] = {"us": tn * 1e6, "frac_of_measured_hbm": T * W * 12 / tn / 1e9 / hbm_gbs}
+            gu = torch.randn(T, FF, device=dev).to(torch.bfloat16)
+            cat = torch.empty(T, FF, dtype=torch.bfloat16, device=dev)
+            tg = time_kernel(lambda: (check(lib.qs_hyb_bias_gelu_tanh(cat.data_ptr(), FF, gu.data_ptr(), FF, ly.mlp_in_bias.data_ptr(), T, FF, 0, raw())), 1)[1],
+                             reps, stream)
+            kern["bias_gelu_tanh"] = {"us": tg * 1e6, "frac_of_measured_hbm": T * FF * 4 / tg / 1e9 / hbm_gbs}
+            del x, upd, gu, cat
+            h = torch.randn(T, W, device=dev).to(torch.bfloat16)
+            ffl = 2 * 3 * W * TOP * moe.ff
+            wb = lambda n: 3 * W * min(E, n * TOP) * moe.ff * 2
+            ff_times(model.layers[1].side_ff, h, lambda l: f"expert_feed_forward_{l}(grouped sigmoid router+sort+gather+2 grouped products+act+combine)", kern, ffl, wb)
+            ff1 = model.layers[1].side_ff
+            route, ti, tw = torch.empty(T, E, device=dev), torch.empty(T, TOP, dtype=torch.int32, device=dev), torch.empty(T, TOP, device=dev)
+            for mode, label in ((1, "router_sigmoid_groups"), (0, "router_softmax(the other design's)")):
+                tr = time_kernel(lambda: (check(lib.qs_hyb_moe_router(route.data_ptr(), ti.data_ptr(), tw.data_ptr(), h.data_ptr(), ff1.w_router.data_ptr(),
+                                                                      T, W, E, TOP, mode, ff1.correction.data_ptr(), 4, 2, 0, raw())), 1)[1], reps, stream)
+                kern[label] = {"us": tr * 1e6, "frac_of_measured_hbm": T * W * 2 / tr / 1e9 / hbm_gbs}
+            # the like feed-forward of the closest design with experts: softmax router, clamped activation, no shared expert, equal sizes
+            tmoe = MoeConfig(E, TOP, FF // TOP, 7.0)
+            tw_ = {k[len("l1.mlp."):]: v for k, v in random_weights(cfg, 1, dev).items() if k.startswith("l1.mlp.")}
+            ff_times(FEED_FORWARDS[MoeConfig](tmoe, tw_, W, torch.bfloat16, dev), h, lambda l: f"expert_feed_forward_{l}(softmax router, clamped activation: the other design's)",
+                     kern, ffl, wb)
+            rec["kernels"] = kern
+            del eng, model, h, tw_, pool, scratch
+        torch.cuda.empty_cache()
+        # ---- the closest existing model at equal size: Rizurax (differential attention | gated delta rule, dense feed-forward)
+        ratt = AttentionMixerConfig(H, G, D, D, RotaryConfig(D // 2, 1e6, 4.0, 4096, 32.0, 1.0), D ** -0.5, maps=2, diff=0.5, head_norm=True)
+        rdlt = DeltaMixerConfig(H, G, D, D, 4)
+        rcfg = HybridConfig("Rizurax", V, W, 1e-5, tuple(HybridLayerConfig(t, m, MlpConfig("dense", FF)) for t, m in
+                                                        (("attention", ratt), ("delta", rdlt), ("attention", ratt), ("delta", rdlt))),
+                            pair_buckets=4093, pair_mul_prev=131, pair_mul_cur=11)
+        with torch.no_grad():
+            model = HybridDecoder(rcfg, random_weights(rcfg, 0, dev), torch.bfloat16, dev)
+            eng = Engine(model, max_tokens=B * (CTX + 64) + NP * LP, max_seqs=B + NP)
+            peer, pb, db = steps(model, eng, V, g)
+            kern = {}
+            tp, td = mixer_times(model.layers[0].mixer, eng.cache.runs[0], pb, db, T)
+            flops = H * pairs * 8 * D
+            kern["attention_prefill(rope+append+attention, 2 maps)"] = {"us": tp * 1e6, "tflops": flops / tp / 1e12, "frac_of_measured_bf16_peak": flops / tp / 1e12 / tflops}
+            kern["attention_decode(rope+append+attention, 2 maps)"] = {"us": td * 1e6, "frac_of_measured_hbm": B * (CTX + 1) * G * 3 * D * 2 / td / 1e9 / hbm_gbs}
+            ly = model.layers[0]
+            x = torch.randn(T, W, device=dev)
+            h1, h2 = torch.empty(T, W, dtype=torch.bfloat16, device=dev), torch.empty(T, W, dtype=torch.bfloat16, device=dev)
+            upd = torch.zeros(T, W, dtype=torch.bfloat16, device=dev)
+            tn = time_kernel(lambda: (check(lib.qs_hyb_rms_norm(h1.data_ptr(), h2.data_ptr(), x.data_ptr(), upd.data_ptr(), ly.norm1.data_ptr(),
+                                                                 ly.norm2.data_ptr(), 1.0, 1e-5, T, W, 0, raw())), 1)[1], reps, stream)
+            kern["add_rms_norm_dual"] = {"us": tn * 1e6, "frac_of_measured_hbm": T * W * 14 / tn / 1e9 / hbm_gbs}
+            gu = torch.randn(T, 2 * FF, device=dev).to(torch.bfloat16)
+            cat = torch.empty(T, FF, dtype=torch.bfloat16, device=dev)
+            tg = time_kernel(lambda: (check(lib.qs_hyb_gelu_tanh_mul(cat.data_ptr(), cat.stride(0), gu.data_ptr(), T, FF, 0, raw())), 1)[1], reps, stream)
+            kern["gelu_tanh_mul"] = {"us": tg * 1e6, "frac_of_measured_hbm": T * FF * 6 / tg / 1e9 / hbm_gbs}
+            peer["kernels"] = kern
+            del eng, model, gu, cat, h1, h2, x, upd
+        torch.cuda.empty_cache()
+        rec["rizurax_equal_size"] = peer
+        out["sizes"][name] = rec
+    print(json.dumps(out), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------------------
 def main():
     args = parse()
     rank = int(os.environ.get("RANK", "0"))
@@ -952,6 +1140,10 @@ def main():
     if args.toderax:
         if rank == 0:
             toderax_block(args)
+        return
+    if args.nusuvik:
+        if rank == 0:
+            nusuvik_block(args)
         return
     if args.impl == "reference-gpu":
         if rank == 0:

@@ -239,9 +239,20 @@ int launch_latent_attention(void* out, const void* qa, const void* pool, const i
 // SHORT: one listed token per block row, the cells shared out over `splits` blocks (blockIdx.z); un-normalised partial sums, running
 //       maximum and denominator go to `part` [n_short][H][splits][2 + K] fp32, latent_merge_kernel finishes.
 // ---------------------------------------------------------------------------------------------------------------------------------
-constexpr int kLtRows = 64, kLtKT = 32, kLtPad = 8, kLtTokensPerSpan = 64;
+constexpr int kLtRows = 64, kLtPad = 8, kLtTokensPerSpan = 64;
 
-template <int NVT, bool SHORT>  // K = 32 NVT: NVT value column blocks of 16 per warp
+// 8 warps = 2 column halves x (RB row blocks of 16 rows x KG = 4 / RB key groups).  With 64 live rows (RB = 4) every warp owns a row block and
+// sees all cells of a tile.  A single token with few heads has 16 or 32 live rows (RB = 1, 2): the warps that would idle take a share of
+// each tile's cells instead (16 cells per warp), keep their own running maximum / denominator / sums and are merged through shared memory
+// at the end -- the per-warp chain of dependent MMAs per tile, which bounds a single token's step, is KG times shorter.
+template <int RB> struct LtShape {
+  static constexpr int KG = 4 / RB;            // key groups
+  static constexpr int KT = KG == 4 ? 64 : 32;  // cells per tile
+  static constexpr int KW = KT / KG;           // cells of a tile per warp: 32, 16, 16
+  static constexpr int QR = 16 * RB;           // query rows held
+};
+
+template <int NVT, int RB, bool SHORT>  // K = 32 NVT: NVT value column blocks of 16 per warp
 __global__ void __launch_bounds__(256, 1) latent_tile_kernel(
     __nv_bfloat16* __restrict__ out, float* __restrict__ part, const __nv_bfloat16* __restrict__ qa, const __nv_bfloat16* __restrict__ pool,
     const int* __restrict__ tile_entry, const int* __restrict__ tile_row0, const int* __restrict__ short_tokens, const int* __restrict__ tok_slot,
@@ -249,12 +260,12 @@ __global__ void __launch_bounds__(256, 1) latent_tile_kernel(
     const int* __restrict__ entry_pos0, const int* __restrict__ block_table, int max_blocks, int T, int H, int HB, int R, float scale, int page,
     int chunk, int window, int splits) {
   extern __shared__ __align__(16) unsigned char smraw[];
-  constexpr int K = 32 * NVT;
+  constexpr int K = 32 * NVT, KG = LtShape<RB>::KG, KT = LtShape<RB>::KT, KW = LtShape<RB>::KW, QR = LtShape<RB>::QR, TPR = 256 / KT;
   const int DK = K + R, DKP = (DK + 15) & ~15, SD = DKP + kLtPad;
-  __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smraw);  // [64][SD]
-  __nv_bfloat16* Ks = Qs + kLtRows * SD;                        // [2][32][SD]
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, rb = warp & 3, ch = warp >> 2;
-  const int RT = kLtRows / HB, h0 = blockIdx.y * HB;
+  __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smraw);  // [QR][SD]
+  __nv_bfloat16* Ks = Qs + QR * SD;                             // [2][KT][SD]
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, ch = warp >> 2, rb = (warp & 3) % RB, kg = (warp & 3) / RB;
+  const int RT = QR / HB, h0 = blockIdx.y * HB;
   int tok0, n_tok, pos0, slot;
   if (SHORT) {
     tok0 = short_tokens[blockIdx.x];
@@ -274,7 +285,7 @@ __global__ void __launch_bounds__(256, 1) latent_tile_kernel(
   const int* bt = block_table + (size_t)slot * max_blocks;
   // queries: 16-byte chunks, zero rows for (token, head) pairs that do not exist, zero columns up to a multiple of 16
   const int dch = DK >> 3, sch = DKP >> 3;
-  for (int c = tid; c < kLtRows * sch; c += 256) {
+  for (int c = tid; c < QR * sch; c += 256) {
     const int r = c / sch, cc = c - r * sch;
     const int tk = r / HB, hh = h0 + r % HB;
     uint4 v = make_uint4(0, 0, 0, 0);
@@ -282,7 +293,7 @@ __global__ void __launch_bounds__(256, 1) latent_tile_kernel(
     *reinterpret_cast<uint4*>(Qs + r * SD + cc * 8) = v;
   }
   const int last_pos = pos0 + n_tok - 1;
-  int kt_lo = first_key(pos0, chunk, window) / kLtKT, kt_hi = last_pos / kLtKT + 1;  // tiles [kt_lo, kt_hi)
+  int kt_lo = first_key(pos0, chunk, window) / KT, kt_hi = last_pos / KT + 1;  // tiles [kt_lo, kt_hi)
   if (SHORT) {
     const int per = (kt_hi - kt_lo + splits - 1) / splits;
     kt_lo += blockIdx.z * per;
@@ -298,21 +309,21 @@ __global__ void __launch_bounds__(256, 1) latent_tile_kernel(
 #pragma unroll
   for (int i = 0; i < 2 * NVT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
-  // 8 threads per cell row, alternating 16-byte chunks; the block-table lookup is made one tile ahead of its use
+  // TPR threads per cell row, alternating 16-byte chunks; the block-table lookup is made one tile ahead of its use
   auto cell_of = [&](int kt) -> long long {
-    const int kp = kt * kLtKT + (tid >> 3);
+    const int kp = kt * KT + tid / TPR;
     return kp <= last_pos ? (long long)bt[kp / page] * page + kp % page : -1;
   };
   auto load_tile = [&](int buf, long long cell) {
-    __nv_bfloat16* Kd = Ks + ((size_t)buf * kLtKT + (tid >> 3)) * SD;
+    __nv_bfloat16* Kd = Ks + ((size_t)buf * KT + tid / TPR) * SD;
     if (cell >= 0) {
       const __nv_bfloat16* src = pool + (size_t)cell * DK;
-      for (int cc = tid & 7; cc < sch; cc += 8) {
+      for (int cc = tid % TPR; cc < sch; cc += TPR) {
         if (cc < dch) cp_async16(Kd + cc * 8, src + cc * 8);
         else *reinterpret_cast<uint4*>(Kd + cc * 8) = make_uint4(0, 0, 0, 0);
       }
     } else {
-      for (int cc = tid & 7; cc < sch; cc += 8) *reinterpret_cast<uint4*>(Kd + cc * 8) = make_uint4(0, 0, 0, 0);
+      for (int cc = tid % TPR; cc < sch; cc += TPR) *reinterpret_cast<uint4*>(Kd + cc * 8) = make_uint4(0, 0, 0, 0);
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
@@ -328,15 +339,15 @@ __global__ void __launch_bounds__(256, 1) latent_tile_kernel(
     }
     __syncthreads();
     if (live) {
-      const __nv_bfloat16* Kc = Ks + (size_t)(kt & 1) * kLtKT * SD;
-      float s[kLtKT / 8][4];
+      const __nv_bfloat16* Kc = Ks + ((size_t)(kt & 1) * KT + kg * KW) * SD;  // this warp's cells of the tile
+      float s[KW / 8][4];
 #pragma unroll
-      for (int i = 0; i < kLtKT / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+      for (int i = 0; i < KW / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
       for (int ks = 0; ks < DKP; ks += 16) {
         uint32_t a[4];
         ldsm_x4(a, Qs + (rb * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * SD + ks + (lane >> 4) * 8);
 #pragma unroll
-        for (int np = 0; np < kLtKT / 16; ++np) {
+        for (int np = 0; np < KW / 16; ++np) {
           uint32_t b[4];
           ldsm_x4(b, Kc + (np * 16 + (lane & 7) + (lane >> 4) * 8) * SD + ks + ((lane >> 3) & 1) * 8);
           mma_bf16(s[2 * np], a, b[0], b[1]);
@@ -345,14 +356,15 @@ __global__ void __launch_bounds__(256, 1) latent_tile_kernel(
       }
       // scale, mask (rows of one warp belong to different tokens: each has its own last and first visible cell), online softmax
       float mx[2] = {-INFINITY, -INFINITY};
-      const bool edge = kt * kLtKT + kLtKT - 1 > warp_qp_min || chunk > 0 || window > 0;
+      const int k0 = kt * KT + kg * KW;
+      const bool edge = k0 + KW - 1 > warp_qp_min || chunk > 0 || window > 0;
 #pragma unroll
-      for (int nt = 0; nt < kLtKT / 8; ++nt)
+      for (int nt = 0; nt < KW / 8; ++nt)
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           float v = s[nt][j] * scale_log2;
           if (edge) {
-            const int kpos = kt * kLtKT + nt * 8 + (lane & 3) * 2 + (j & 1);
+            const int kpos = k0 + nt * 8 + (lane & 3) * 2 + (j & 1);
             if (kpos > qp[j >> 1] || kpos < fk[j >> 1]) v = -INFINITY;
           }
           s[nt][j] = v;
@@ -369,7 +381,7 @@ __global__ void __launch_bounds__(256, 1) latent_tile_kernel(
         l_run[r] *= corr[r];
       }
 #pragma unroll
-      for (int nt = 0; nt < kLtKT / 8; ++nt)
+      for (int nt = 0; nt < KW / 8; ++nt)
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           const float mm = m_run[j >> 1];
@@ -384,7 +396,7 @@ __global__ void __launch_bounds__(256, 1) latent_tile_kernel(
       constexpr int NVG = NVT % 4 == 0 ? 4 : (NVT % 2 == 0 ? 2 : 1);
       const __nv_bfloat16* Vc = Kc + ch * (K / 2);  // the values: this warp's half of the cells' first K columns
 #pragma unroll
-      for (int kk = 0; kk < kLtKT / 16; ++kk) {
+      for (int kk = 0; kk < KW / 16; ++kk) {
         uint32_t a[3][4];
 #pragma unroll
         for (int pt = 0; pt < 4; ++pt) {
@@ -411,12 +423,45 @@ __global__ void __launch_bounds__(256, 1) latent_tile_kernel(
     }
     __syncthreads();  // every warp is done with this buffer before tile kt + 2 streams into it
   }
-  if (!live) return;
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
     l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
     l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
   }
+  if (KG > 1) {
+    // the key groups of a row block meet in shared memory (the tiles are consumed): group 0 folds the others' (maximum, denominator, sums)
+    constexpr int PER = 4 + 8 * NVT;  // floats per thread
+    float* xs = reinterpret_cast<float*>(smraw);
+    __syncthreads();  // a block without tiles comes here straight from writing the queries
+    if (kg > 0) {
+      float* d = xs + ((size_t)((ch * RB + rb) * (KG - 1) + kg - 1) * 32 + lane) * PER;
+      d[0] = m_run[0]; d[1] = m_run[1]; d[2] = l_run[0]; d[3] = l_run[1];
+#pragma unroll
+      for (int i = 0; i < 2 * NVT; ++i) *reinterpret_cast<float4*>(d + 4 + 4 * i) = make_float4(o[i][0], o[i][1], o[i][2], o[i][3]);
+    }
+    __syncthreads();
+    if (kg > 0) return;
+#pragma unroll
+    for (int g = 1; g < KG; ++g) {
+      const float* d = xs + ((size_t)((ch * RB + rb) * (KG - 1) + g - 1) * 32 + lane) * PER;
+      float fa[2], fb[2];
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        const float mo = d[r], m_new = fmaxf(m_run[r], mo);
+        fa[r] = m_new == -INFINITY ? 1.f : fast_exp2(m_run[r] - m_new);
+        fb[r] = m_new == -INFINITY ? 0.f : fast_exp2(mo - m_new);
+        m_run[r] = m_new;
+        l_run[r] = l_run[r] * fa[r] + d[2 + r] * fb[r];
+      }
+#pragma unroll
+      for (int i = 0; i < 2 * NVT; ++i) {
+        const float4 v = *reinterpret_cast<const float4*>(d + 4 + 4 * i);
+        o[i][0] = o[i][0] * fa[0] + v.x * fb[0]; o[i][1] = o[i][1] * fa[0] + v.y * fb[0];
+        o[i][2] = o[i][2] * fa[1] + v.z * fb[1]; o[i][3] = o[i][3] * fa[1] + v.w * fb[1];
+      }
+    }
+  }
+  if (!live) return;
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
     const int row = qrow + r * 8, tk = row / HB, hh = h0 + row % HB;
@@ -465,14 +510,23 @@ __global__ void latent_merge_kernel(__nv_bfloat16* __restrict__ out, const float
   }
 }
 
-constexpr int kLtTargetBlocks = 296;  // key shares of single tokens are chosen to give about two blocks per SM
+// key shares of single tokens are chosen to give about one block per SM (148): a block of the widest latents takes most of an SM's shared
+// memory, so a second wave of blocks would wait for the first (measured at 64 tokens x 1024 cells: 55 us against 63 us with twice the blocks)
+constexpr int kLtTargetBlocks = 148;
 constexpr int kLtMaxSplits = 16;
+
+template <int RB> size_t latent_tile_smem(int K, int R) {
+  const int sd = ((K + R + 15) & ~15) + kLtPad;
+  const size_t tiles = (size_t)(LtShape<RB>::QR + 2 * LtShape<RB>::KT) * sd * sizeof(__nv_bfloat16);
+  const size_t merge = (size_t)2 * RB * (LtShape<RB>::KG - 1) * 32 * (4 + K / 4) * sizeof(float);  // the key groups' meeting place
+  return std::max(tiles, merge);
+}
 
 bool latent_fast_supported(int dtype, int heads, int kv_rank, int rot_dim) {
   if (dtype != QS_DTYPE_BF16 || heads < 1 || rot_dim < 0) return false;
   if (!(kv_rank == 32 || kv_rank == 64 || kv_rank == 128 || kv_rank == 256 || kv_rank == 512)) return false;
-  const int dkp = (kv_rank + rot_dim + 15) & ~15;
-  return (kv_rank + rot_dim) % 8 == 0 && (size_t)(kLtRows + 2 * kLtKT) * (dkp + kLtPad) * 2 <= 200 * 1024;
+  const size_t most = std::max(latent_tile_smem<1>(kv_rank, rot_dim), std::max(latent_tile_smem<2>(kv_rank, rot_dim), latent_tile_smem<4>(kv_rank, rot_dim)));
+  return (kv_rank + rot_dim) % 8 == 0 && most <= 200 * 1024;
 }
 
 int latent_head_block(int heads) { return heads <= 16 ? 16 : (heads <= 32 ? 32 : 64); }
@@ -482,32 +536,50 @@ int latent_splits(int n_short, int heads) {
   return std::max(1, std::min(kLtMaxSplits, kLtTargetBlocks / std::max(1, n_short * groups)));
 }
 
+template <int NVT, int RB>
+int launch_latent_short(void* out, float* part, const void* qa, const void* pool, const int* short_tokens, int n_short, const int* tok_slot,
+                        const int* tok_pos, const int* block_table, int max_blocks, int T, int H, int HB, int R, float scale, int page, int chunk,
+                        int window, cudaStream_t s) {
+  const int K = 32 * NVT, groups = (H + HB - 1) / HB, splits = latent_splits(n_short, H);
+  const size_t smem = latent_tile_smem<RB>(K, R);
+  static bool attr_set[kMaxDevices] = {};
+  if (!attr_set[device_ordinal()]) {
+    if (int rc = check_cuda(cudaFuncSetAttribute(latent_tile_kernel<NVT, RB, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024), "latent tiles smem")) return rc;
+    attr_set[device_ordinal()] = true;
+  }
+  latent_tile_kernel<NVT, RB, true><<<dim3(n_short, groups, splits), 256, smem, s>>>(
+      (__nv_bfloat16*)out, part, (const __nv_bfloat16*)qa, (const __nv_bfloat16*)pool, nullptr, nullptr, short_tokens, tok_slot, tok_pos, nullptr, nullptr,
+      nullptr, nullptr, block_table, max_blocks, T, H, HB, R, scale, page, chunk, window, splits);
+  const int warps = n_short * H;
+  latent_merge_kernel<<<(warps + 3) / 4, 128, 0, s>>>((__nv_bfloat16*)out, part, short_tokens, n_short, T, H, K, splits);
+  return check_cuda(cudaGetLastError(), "hyb_latent_attention_fast single tokens");
+}
+
 template <int NVT>
 int launch_latent_tiles(void* out, float* part, const void* qa, const void* pool, const int* tile_entry, const int* tile_row0, int n_tiles,
                         const int* short_tokens, int n_short, const int* tok_slot, const int* tok_pos, const int* entry_start, const int* entry_len,
                         const int* entry_slot, const int* entry_pos0, const int* block_table, int max_blocks, int T, int H, int R, float scale,
                         int page, int chunk, int window, cudaStream_t s) {
-  const int K = 32 * NVT, HB = latent_head_block(H), groups = (H + HB - 1) / HB, dkp = (K + R + 15) & ~15;
-  const size_t smem = (size_t)(kLtRows + 2 * kLtKT) * (dkp + kLtPad) * sizeof(__nv_bfloat16);
-  static bool attr_set[kMaxDevices] = {};
-  if (!attr_set[device_ordinal()]) {
-    if (int rc = check_cuda(cudaFuncSetAttribute(latent_tile_kernel<NVT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024), "latent tiles smem")) return rc;
-    if (int rc = check_cuda(cudaFuncSetAttribute(latent_tile_kernel<NVT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024), "latent tiles smem")) return rc;
-    attr_set[device_ordinal()] = true;
-  }
-  if (n_tiles > 0)
-    latent_tile_kernel<NVT, false><<<dim3(n_tiles * (kLtTokensPerSpan / (kLtRows / HB)), groups), 256, smem, s>>>(
+  const int K = 32 * NVT, HB = latent_head_block(H), groups = (H + HB - 1) / HB;
+  if (n_tiles > 0) {
+    const size_t smem = latent_tile_smem<4>(K, R);
+    static bool attr_set[kMaxDevices] = {};
+    if (!attr_set[device_ordinal()]) {
+      if (int rc = check_cuda(cudaFuncSetAttribute(latent_tile_kernel<NVT, 4, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024), "latent tiles smem")) return rc;
+      attr_set[device_ordinal()] = true;
+    }
+    latent_tile_kernel<NVT, 4, false><<<dim3(n_tiles * (kLtTokensPerSpan / (kLtRows / HB)), groups), 256, smem, s>>>(
         (__nv_bfloat16*)out, nullptr, (const __nv_bfloat16*)qa, (const __nv_bfloat16*)pool, tile_entry, tile_row0, nullptr, tok_slot, tok_pos, entry_start,
         entry_len, entry_slot, entry_pos0, block_table, max_blocks, T, H, HB, R, scale, page, chunk, window, 1);
-  if (n_short > 0) {
-    const int splits = latent_splits(n_short, H);
-    latent_tile_kernel<NVT, true><<<dim3(n_short, groups, splits), 256, smem, s>>>(
-        (__nv_bfloat16*)out, part, (const __nv_bfloat16*)qa, (const __nv_bfloat16*)pool, nullptr, nullptr, short_tokens, tok_slot, tok_pos, entry_start,
-        entry_len, entry_slot, entry_pos0, block_table, max_blocks, T, H, HB, R, scale, page, chunk, window, splits);
-    const int warps = n_short * H;
-    latent_merge_kernel<<<(warps + 3) / 4, 128, 0, s>>>((__nv_bfloat16*)out, part, short_tokens, n_short, T, H, K, splits);
+    if (int rc = check_cuda(cudaGetLastError(), "hyb_latent_attention_fast tiles")) return rc;
   }
-  return check_cuda(cudaGetLastError(), "hyb_latent_attention_fast");
+  if (n_short > 0) {
+    // a single token has HB live rows: 16 (one row block, four key groups), 32 (two and two) or 64 (four row blocks)
+    if (HB == 16) return launch_latent_short<NVT, 1>(out, part, qa, pool, short_tokens, n_short, tok_slot, tok_pos, block_table, max_blocks, T, H, HB, R, scale, page, chunk, window, s);
+    if (HB == 32) return launch_latent_short<NVT, 2>(out, part, qa, pool, short_tokens, n_short, tok_slot, tok_pos, block_table, max_blocks, T, H, HB, R, scale, page, chunk, window, s);
+    return launch_latent_short<NVT, 4>(out, part, qa, pool, short_tokens, n_short, tok_slot, tok_pos, block_table, max_blocks, T, H, HB, R, scale, page, chunk, window, s);
+  }
+  return qs::QS_OK;
 }
 
 // out[t][h * Dv + j] = ov[h][t][j] * sigmoid(gate[t][col_g + h])   (gate == null: no gate).  One block per token.

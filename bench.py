@@ -978,7 +978,8 @@ def nusuvik_block(args):
         prompts = [torch.randint(0, V, (LP,), generator=g).tolist() for _ in range(NP)]
         for i, p_ in enumerate(prompts):
             eng.cache.admit(("p", i)); eng.cache.reserve(("p", i), LP)
-        pb = StepBatch.build([(eng.cache.seqs[("p", i)].slot, 0, -1, p_) for i, p_ in enumerate(prompts)], eng.cache.sync_block_table(), dev)
+        pb = StepBatch.build([(eng.cache.seqs[("p", i)].slot, 0, -1, p_) for i, p_ in enumerate(prompts)], eng.cache.sync_block_table(), dev,
+                             eng.cache.page_size)
         t = time_kernel(lambda: (model.forward(pb, eng.cache), 1)[1], reps, stream)
         rec = {"prefill": {"tokens": NP * LP, "ms": t * 1e3, "tokens_per_s": NP * LP / t}}
         for i in range(B):
@@ -1021,9 +1022,17 @@ def nusuvik_block(args):
             tp, td = mixer_times(mx, eng.cache.runs[0], pb, db, T)
             # useful work: scores and weighted values of heads of size (D + R) and D; executed: the same over the latent's K + R and K numbers
             useful, executed = H * pairs * 2 * (D + R + D), H * pairs * 2 * (KR + R + KR)
-            kern["latent_attention_prefill(norms+append+q up+key up+rotate+attention+value up+gate)"] = {
-                "us": tp * 1e6, "useful_tflops": useful / tp / 1e12, "executed_tflops": executed / tp / 1e12,
-                "frac_of_measured_bf16_peak_useful": useful / tp / 1e12 / tflops, "frac_of_measured_bf16_peak_executed": executed / tp / 1e12 / tflops}
+            kern["latent_attention_prefill(norms+append+q up+rotate+keys and values of every head+per-head tile attention+gate)"] = {
+                "us": tp * 1e6, "tflops": useful / tp / 1e12, "frac_of_measured_bf16_peak": useful / tp / 1e12 / tflops}
+            import qserve_b200.hybrid as hyb_mod
+            hyb_mod.LATENT_IMPL = "latent"
+            try:
+                tl, _ = mixer_times(mx, eng.cache.runs[0], pb, db, T)
+            finally:
+                hyb_mod.LATENT_IMPL = None
+            kern["latent_attention_prefill, kept in the latent space(norms+append+q up+key up+rotate+latent tiles+value up+gate)"] = {
+                "us": tl * 1e6, "useful_tflops": useful / tl / 1e12, "executed_tflops": executed / tl / 1e12,
+                "frac_of_measured_bf16_peak_useful": useful / tl / 1e12 / tflops, "frac_of_measured_bf16_peak_executed": executed / tl / 1e12 / tflops}
             kern["latent_attention_decode(the same)"] = {"us": td * 1e6, "frac_of_measured_hbm": B * (CTX + 1) * (KR + R) * 2 / td / 1e9 / hbm_gbs}
             # the attention kernels alone
             qa = torch.randn(T, H, KR + R, device=dev).to(torch.bfloat16)

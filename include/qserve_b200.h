@@ -348,9 +348,10 @@ QS_API int qs_hyb_latent_prepare(void* cq, const void* proj, int64_t stride, int
                                  const int32_t* block_table, int max_blocks, void* pool, int tokens_n, int q_rank, int kv_rank, int rot_dim,
                                  int page_size, float eps, int dtype, void* stream);
 /* qa [tokens, heads, kv_rank + rot_dim] = [qlat[head, token, :] | rotated q[token, head * (dim + rot_dim) + dim ...]]: the queries as they are
- * scored against the cells (qlat [heads, tokens, kv_rank]: the unrotated query parts taken through the heads' key up-projections) */
-QS_API int qs_hyb_latent_query(void* qa, const void* qlat, const void* q, int64_t q_stride, const float* inv_freq, int rot_dims,
-                               const int32_t* tok_pos, int tokens_n, int heads, int dim, int kv_rank, int rot_dim, int dtype, void* stream);
+ * scored against the cells (qlat [heads, tokens, kv_rank]: the unrotated query parts taken through the heads' key up-projections).  qa may be
+ * NULL.  rotate_back: the rotated part also replaces q's own. */
+QS_API int qs_hyb_latent_query(void* qa, const void* qlat, void* q, int64_t q_stride, const float* inv_freq, int rot_dims, const int32_t* tok_pos,
+                               int tokens_n, int heads, int dim, int kv_rank, int rot_dim, int rotate_back, int dtype, void* stream);
 /* out [heads, tokens, kv_rank] = softmax-weighted sum of the cells' first kv_rank numbers over positions first..tok_pos (first as in
  * qs_hyb_attention), scores scale * qa . cell in fp32.  Any shape with kv_rank <= 512. */
 QS_API int qs_hyb_latent_attention(void* out, const void* qa, const void* pool, const int32_t* tok_slot, const int32_t* tok_pos,
@@ -368,9 +369,11 @@ QS_API int qs_hyb_latent_attention_fast(void* out, const void* qa, const void* p
                                         const int32_t* entry_len, const int32_t* entry_slot, const int32_t* entry_pos0, int tokens_n,
                                         float* scratch, int heads, int kv_rank, int rot_dim, float scale, int page_size, int chunk, int window,
                                         int dtype, void* stream);
-/* out[t, h * vdim + j] = ov[h, t, j] * sigmoid(gate[t, col_g + h]) (gate may be NULL: no gate); ov [heads, tokens, vdim] */
-QS_API int qs_hyb_latent_gate_out(void* out, int64_t out_stride, const void* ov, const void* gate, int64_t gate_stride, int col_g, int tokens_n,
-                                  int heads, int vdim, int dtype, void* stream);
+/* out[t, h * vdim + j] = o * sigmoid(gate[t, col_g + h]) (gate may be NULL: no gate); o = ov[h, t, j] (ov [heads, tokens, vdim]) or, for tokens
+ * of entries of at least min_long tokens when alt is given, alt[t, h * vdim + j] */
+QS_API int qs_hyb_latent_gate_out(void* out, int64_t out_stride, const void* ov, const void* alt, int64_t alt_stride, const int32_t* tok_entry,
+                                  const int32_t* entry_len, int min_long, const void* gate, int64_t gate_stride, int col_g, int tokens_n, int heads,
+                                  int vdim, int dtype, void* stream);
 
 #ifdef __cplusplus
 }

@@ -79,13 +79,13 @@ SIGNATURES = {
     "qs_hyb_softcap": (c_int, [_P, _L, _F, _P]),
     # csrc/hybrid_latent.cu
     "qs_hyb_latent_prepare": (c_int, [_P, _P, _L, _I, _I, _P, _P, _P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _F, _I, _P]),
-    "qs_hyb_latent_query": (c_int, [_P, _P, _P, _L, _P, _I, _P, _I, _I, _I, _I, _I, _I, _P]),
+    "qs_hyb_latent_query": (c_int, [_P, _P, _P, _L, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _P]),
     "qs_hyb_latent_attention": (c_int, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _I, _P]),
     "qs_hyb_latent_attention_fast_supported": (c_int, [_I, _I, _I, _I]),
     "qs_hyb_latent_attention_scratch_floats": (_L, [_I, _I, _I]),
     "qs_hyb_latent_attention_fast": (c_int, [_P, _P, _P, _P, _P, _P, _I, _P, _P, _I, _P, _I, _P, _P, _P, _P, _I, _P, _I, _I, _I, _F, _I, _I, _I, _I,
                                              _P]),
-    "qs_hyb_latent_gate_out": (c_int, [_P, _L, _P, _P, _L, _I, _I, _I, _I, _I, _P]),
+    "qs_hyb_latent_gate_out": (c_int, [_P, _L, _P, _P, _L, _P, _P, _I, _P, _L, _I, _I, _I, _I, _I, _P]),
 }
 
 ABI_VERSION = 1

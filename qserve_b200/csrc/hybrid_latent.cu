@@ -76,28 +76,37 @@ __global__ void __launch_bounds__(128) latent_prepare_kernel(ST* __restrict__ cq
   }
 }
 
-// query rows of K + R numbers: qa[t][h] = [qlat[h][t][0:K] | rotate(q[t][h][D : D + R])].  One block per (token, head).
+// query rows of K + R numbers: qa[t][h] = [qlat[h][t][0:K] | rotate(q[t][h][D : D + R])] (qa may be null).  rotate_back: the rotated part
+// also replaces q's own (the per-head keys of a prompt portion are scored against q as it lies).  One block per (token, head); a thread
+// takes both entries of a rotated pair.
 template <typename ST>
-__global__ void __launch_bounds__(64) latent_query_kernel(ST* __restrict__ qa, const ST* __restrict__ qlat, const ST* __restrict__ q, long long q_stride,
+__global__ void __launch_bounds__(64) latent_query_kernel(ST* __restrict__ qa, const ST* __restrict__ qlat, ST* __restrict__ q, long long q_stride,
                                                           const float* __restrict__ inv_freq, int rot_dims, const int* __restrict__ tok_pos, int T, int H,
-                                                          int D, int K, int R) {
+                                                          int D, int K, int R, int rotate_back) {
   const int t = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
-  ST* dst = qa + ((size_t)t * H + h) * (size_t)(K + R);
-  const ST* src = qlat + ((size_t)h * T + t) * (size_t)K;
-  for (int i = tid; i < K; i += blockDim.x) dst[i] = src[i];
-  const ST* qr = q + (size_t)t * q_stride + (size_t)h * (D + R) + D;
-  const int pos = tok_pos[t], half = rot_dims >> 1;
-  for (int i = tid; i < R; i += blockDim.x) {
-    float v = ldf(qr + i);
-    if (i < rot_dims) {
-      const int p = i < half ? i : i - half;
-      float s, c;
-      sincosf((float)pos * inv_freq[p], &s, &c);
-      const float a = ldf(qr + p), b = ldf(qr + p + half);
-      v = i < half ? a * c - b * s : b * c + a * s;
-    }
-    stf(dst + K + i, v);
+  ST* dst = qa != nullptr ? qa + ((size_t)t * H + h) * (size_t)(K + R) : nullptr;
+  if (dst != nullptr) {
+    const ST* src = qlat + ((size_t)h * T + t) * (size_t)K;
+    for (int i = tid; i < K; i += blockDim.x) dst[i] = src[i];
   }
+  ST* qr = q + (size_t)t * q_stride + (size_t)h * (D + R) + D;
+  const int pos = tok_pos[t], half = rot_dims >> 1;
+  for (int p = tid; p < half; p += blockDim.x) {
+    float s, c;
+    sincosf((float)pos * inv_freq[p], &s, &c);
+    const float a = ldf(qr + p), b = ldf(qr + p + half);
+    const float u = a * c - b * s, v = b * c + a * s;
+    if (dst != nullptr) {
+      stf(dst + K + p, u);
+      stf(dst + K + p + half, v);
+    }
+    if (rotate_back) {
+      stf(qr + p, u);
+      stf(qr + p + half, v);
+    }
+  }
+  if (dst != nullptr)
+    for (int i = rot_dims + tid; i < R; i += blockDim.x) dst[K + i] = qr[i];
 }
 
 // ---------------------------------------------------------------------------------------------------------------------------------
@@ -582,14 +591,18 @@ int launch_latent_tiles(void* out, float* part, const void* qa, const void* pool
   return qs::QS_OK;
 }
 
-// out[t][h * Dv + j] = ov[h][t][j] * sigmoid(gate[t][col_g + h])   (gate == null: no gate).  One block per token.
+// out[t][h * Dv + j] = o * sigmoid(gate[t][col_g + h])   (gate == null: no gate).  o = ov[h][t][j] (head-major rows of the value
+// up-projection), or, for tokens of entries of at least min_long tokens when `alt` is given, alt[t][h * Dv + j] (token-major rows of the
+// per-head attention over a prompt portion).  One block per token.
 template <typename ST>
-__global__ void latent_gate_out_kernel(ST* __restrict__ out, long long out_stride, const ST* __restrict__ ov, const ST* __restrict__ gate,
-                                       long long gate_stride, int col_g, int T, int H, int Dv) {
+__global__ void latent_gate_out_kernel(ST* __restrict__ out, long long out_stride, const ST* __restrict__ ov, const ST* __restrict__ alt,
+                                       long long alt_stride, const int* __restrict__ tok_entry, const int* __restrict__ entry_len, int min_long,
+                                       const ST* __restrict__ gate, long long gate_stride, int col_g, int T, int H, int Dv) {
   const int t = blockIdx.x;
+  const bool from_alt = alt != nullptr && entry_len[tok_entry[t]] >= min_long;
   for (int i = threadIdx.x; i < H * Dv; i += blockDim.x) {
     const int h = i / Dv, j = i - h * Dv;
-    float v = ldf(ov + ((size_t)h * T + t) * Dv + j);
+    float v = from_alt ? ldf(alt + (size_t)t * alt_stride + i) : ldf(ov + ((size_t)h * T + t) * Dv + j);
     if (gate != nullptr) v *= 1.f / (1.f + expf(-ldf(gate + (size_t)t * gate_stride + col_g + h)));
     stf(out + (size_t)t * out_stride + i, v);
   }
@@ -628,18 +641,18 @@ int qs_hyb_latent_prepare(void* cq, const void* proj, int64_t stride, int col_q,
   return check_cuda(cudaGetLastError(), "hyb_latent_prepare");
 }
 
-int qs_hyb_latent_query(void* qa, const void* qlat, const void* q, int64_t q_stride, const float* inv_freq, int rot_dims, const int32_t* tok_pos,
-                        int tokens_n, int heads, int dim, int kv_rank, int rot_dim, int dtype, void* stream) {
-  QS_REQUIRE(qa && qlat && q && tok_pos, "hyb_latent_query: null tensor");
+int qs_hyb_latent_query(void* qa, const void* qlat, void* q, int64_t q_stride, const float* inv_freq, int rot_dims, const int32_t* tok_pos,
+                        int tokens_n, int heads, int dim, int kv_rank, int rot_dim, int rotate_back, int dtype, void* stream) {
+  QS_REQUIRE(q && tok_pos && (qa == nullptr || qlat != nullptr) && (qa != nullptr || rotate_back), "hyb_latent_query: null tensor");
   QS_REQUIRE(rot_dims % 2 == 0 && rot_dims >= 0 && rot_dims <= rot_dim && (rot_dims == 0 || inv_freq), "hyb_latent_query: bad rotation");
   if (tokens_n == 0) return qs::QS_OK;
   cudaStream_t s = (cudaStream_t)stream;
   dim3 grid(tokens_n, heads);
   QS_DT(dtype,
-        (latent_query_kernel<__nv_bfloat16><<<grid, 64, 0, s>>>((__nv_bfloat16*)qa, (const __nv_bfloat16*)qlat, (const __nv_bfloat16*)q, q_stride, inv_freq,
-                                                                 rot_dims, tok_pos, tokens_n, heads, dim, kv_rank, rot_dim)),
-        (latent_query_kernel<float><<<grid, 64, 0, s>>>((float*)qa, (const float*)qlat, (const float*)q, q_stride, inv_freq, rot_dims, tok_pos, tokens_n,
-                                                         heads, dim, kv_rank, rot_dim)));
+        (latent_query_kernel<__nv_bfloat16><<<grid, 64, 0, s>>>((__nv_bfloat16*)qa, (const __nv_bfloat16*)qlat, (__nv_bfloat16*)q, q_stride, inv_freq, rot_dims,
+                                                                 tok_pos, tokens_n, heads, dim, kv_rank, rot_dim, rotate_back)),
+        (latent_query_kernel<float><<<grid, 64, 0, s>>>((float*)qa, (const float*)qlat, (float*)q, q_stride, inv_freq, rot_dims, tok_pos, tokens_n, heads, dim,
+                                                         kv_rank, rot_dim, rotate_back)));
   return check_cuda(cudaGetLastError(), "hyb_latent_query");
 }
 
@@ -698,16 +711,20 @@ int qs_hyb_latent_attention_fast(void* out, const void* qa, const void* pool, co
 #undef QS_LT
 }
 
-int qs_hyb_latent_gate_out(void* out, int64_t out_stride, const void* ov, const void* gate, int64_t gate_stride, int col_g, int tokens_n, int heads,
-                           int vdim, int dtype, void* stream) {
-  QS_REQUIRE(out && ov, "hyb_latent_gate_out: null tensor");
+int qs_hyb_latent_gate_out(void* out, int64_t out_stride, const void* ov, const void* alt, int64_t alt_stride, const int32_t* tok_entry,
+                           const int32_t* entry_len, int min_long, const void* gate, int64_t gate_stride, int col_g, int tokens_n, int heads, int vdim,
+                           int dtype, void* stream) {
+  QS_REQUIRE(out && (ov || alt), "hyb_latent_gate_out: null tensor");
+  QS_REQUIRE(alt == nullptr || (tok_entry && entry_len), "hyb_latent_gate_out: the second source needs the entry tables");
+  QS_REQUIRE(ov != nullptr || min_long <= 1, "hyb_latent_gate_out: without head-major rows every token must come from the second source");
   if (tokens_n == 0) return qs::QS_OK;
   cudaStream_t s = (cudaStream_t)stream;
   QS_DT(dtype,
-        (latent_gate_out_kernel<__nv_bfloat16><<<tokens_n, 128, 0, s>>>((__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)ov, (const __nv_bfloat16*)gate,
-                                                                         gate_stride, col_g, tokens_n, heads, vdim)),
-        (latent_gate_out_kernel<float><<<tokens_n, 128, 0, s>>>((float*)out, out_stride, (const float*)ov, (const float*)gate, gate_stride, col_g, tokens_n,
-                                                                heads, vdim)));
+        (latent_gate_out_kernel<__nv_bfloat16><<<tokens_n, 128, 0, s>>>((__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)ov, (const __nv_bfloat16*)alt,
+                                                                         alt_stride, tok_entry, entry_len, min_long, (const __nv_bfloat16*)gate, gate_stride,
+                                                                         col_g, tokens_n, heads, vdim)),
+        (latent_gate_out_kernel<float><<<tokens_n, 128, 0, s>>>((float*)out, out_stride, (const float*)ov, (const float*)alt, alt_stride, tok_entry, entry_len,
+                                                                min_long, (const float*)gate, gate_stride, col_g, tokens_n, heads, vdim)));
   return check_cuda(cudaGetLastError(), "hyb_latent_gate_out");
 }
 

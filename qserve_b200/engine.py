@@ -155,7 +155,7 @@ class Engine:
             all_logits = self._decode_step(rows, table)
             graphed = all_logits is not None
         if not graphed:
-            x = self.model.forward(StepBatch.build(rows, table, self.model.device), cache, tap)
+            x = self.model.forward(StepBatch.build(rows, table, self.model.device, cache.page_size), cache, tap)
         for sid, toks, _ in entries:
             st = cache.seqs[sid]
             st.length += len(toks)

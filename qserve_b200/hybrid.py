@@ -75,6 +75,13 @@ class StepBatch:
     long_tokens: Optional[torch.Tensor] = None   # int32 [n_long] rows covered by tiles
     short_tokens: Optional[torch.Tensor] = None  # int32 [n_short] all other rows
 
+    # entries of at least TILE_MIN tokens, when `build` is told the page size: their sequences' pages so far, numbered in one run, so that a
+    # mixer can lay out per-step copies of what those pages hold (page i of the run is the sequence's page ctx_src[i]; ctx_table is a block
+    # table into the run)
+    n_ctx_pages: int = 0
+    ctx_src: Optional[torch.Tensor] = None     # int64 [n_ctx_pages] page of the pool
+    ctx_table: Optional[torch.Tensor] = None   # int32 [slots, max_blocks]
+
     TILE_MIN = 16
     TILE_ROWS = 64
 
@@ -118,11 +125,25 @@ class StepBatch:
         return StepBatch(T, E, *v, block_table, nt, n_long, n_short, d[o:o + nt], d[o + nt:o + 2 * nt], d[5 * T:5 * T + n_long], d[5 * T + n_long:6 * T])
 
     @staticmethod
-    def build(entries: Sequence[tuple], block_table: torch.Tensor, device: torch.device) -> "StepBatch":
+    def build(entries: Sequence[tuple], block_table: torch.Tensor, device: torch.device, page_size: int = 0) -> "StepBatch":
         host, sizes = StepBatch.pack(entries)
         if device.type == "cuda":
             host = host.pin_memory()
-        return StepBatch.view(host.to(device, non_blocking=True), sizes, block_table)
+        b = StepBatch.view(host.to(device, non_blocking=True), sizes, block_table)
+        if page_size > 0:
+            slots, idx = [], []
+            for s, p0, _, toks in entries:
+                if len(toks) >= StepBatch.TILE_MIN:
+                    n = -(-(p0 + len(toks)) // page_size)
+                    slots += [s] * n
+                    idx += range(n)
+            if slots:
+                cs, ci = torch.tensor(slots, dtype=torch.int64).to(device), torch.tensor(idx, dtype=torch.int64).to(device)
+                b.n_ctx_pages = len(slots)
+                b.ctx_src = block_table[cs, ci].to(torch.int64)
+                b.ctx_table = torch.zeros_like(block_table)
+                b.ctx_table[cs, ci] = torch.arange(len(slots), dtype=block_table.dtype, device=device)
+        return b
 
 
 # ------------------------------------------------------------------------------------------------------------------------
@@ -339,6 +360,14 @@ class LatentAttentionMixer(_Mixer):
         self.w_uk = st(w["uk"]).view(H, D, K)                                   # q_lat[h] = q_nope[h] @ w_uk[h]
         self.w_uv = st(w["uv"].reshape(H, Dv, K).transpose(1, 2))               # [H, K, Dv]: values[h] = o_lat[h] @ w_uv[h]
         self.w_out = w["o"]
+        # prompt portions: keys [W_uk,h c | k_rot] and values W_uv,h c of every head are laid out per step from the cached rows (one product
+        # each; the identity block passes the shared rotated part into every head's key), and the per-head tile kernels run on them
+        aug = torch.zeros((H, D + R, K + R), dtype=torch.float32)
+        aug[:, :D, :K] = w["uk"].to(torch.float32).reshape(H, D, K)
+        aug[:, D:, K:] = torch.eye(R)
+        self.w_keys = st(aug.reshape(H * (D + R), K + R))
+        self.w_values = st(w["uv"])
+        self.per_head_ok = lib.qs_hyb_attention_fast_supported(_DT[dtype], H, H, 1, D + R, Dv, H * (D + R)) == 1
         self.gain_q, self.gain_kv = f32(w["dq.norm"]), f32(w["dkv.norm"])
         if m.rot is not None and (m.rot.layout != "half" or m.rot.factor is not None):
             raise ValueError("latent attention rotates pairs (i, i + dims/2) with unscaled frequencies")
@@ -346,7 +375,8 @@ class LatentAttentionMixer(_Mixer):
         self.rot_dims = m.rot.dims if m.rot is not None else 0
 
     def scratch_floats(self, tokens: int) -> int:
-        return int(lib.qs_hyb_latent_attention_scratch_floats(tokens, self.m.heads, self.m.kv_rank))
+        per_head = int(lib.qs_hyb_attention_scratch_floats(tokens, self.m.heads, self.m.heads, 1, self.m.vdim)) if self.per_head_ok else 0
+        return max(int(lib.qs_hyb_latent_attention_scratch_floats(tokens, self.m.heads, self.m.kv_rank)), per_head)
 
     def run(self, proj: torch.Tensor, out: torch.Tensor, b: StepBatch, run_cache: dict, page_size: int, scratch, dt: int, stream) -> None:
         m, T, dev = self.m, b.n_tokens, proj.device
@@ -357,25 +387,43 @@ class LatentAttentionMixer(_Mixer):
                                         self.gain_kv.data_ptr(), _p(self.inv_freq), self.rot_dims, _p(b.tok_slot), _p(b.tok_pos), _p(b.block_table),
                                         b.block_table.shape[1], pool.data_ptr(), T, Q, K, R, page_size, self.eps, dt, stream))
         q = torch.mm(cq, self.w_uq.t())                                          # [T, H (D + R)]
-        qlat = torch.bmm(q.view(T, H, D + R)[:, :, :D].transpose(0, 1), self.w_uk)  # [H, T, K]
-        qa = torch.empty((T, H, K + R), dtype=proj.dtype, device=dev)
-        check(lib.qs_hyb_latent_query(qa.data_ptr(), qlat.data_ptr(), q.data_ptr(), q.stride(0), _p(self.inv_freq), self.rot_dims, _p(b.tok_pos), T, H,
-                                      D, K, R, dt, stream))
-        olat = torch.empty((H, T, K), dtype=proj.dtype, device=dev)
-        if scratch is not None and LATENT_IMPL != "plain" and lib.qs_hyb_latent_attention_fast_supported(dt, H, K, R) == 1:
-            check(lib.qs_hyb_latent_attention_fast(olat.data_ptr(), qa.data_ptr(), pool.data_ptr(), _p(b.tok_slot), _p(b.tok_pos), _p(b.block_table),
-                                                   b.block_table.shape[1], _p(b.tile_entry), _p(b.tile_row0), b.n_tiles, _p(b.short_tokens), b.n_short,
-                                                   _p(b.entry_start), _p(b.entry_len), _p(b.entry_slot), _p(b.entry_pos0), T, scratch.data_ptr(), H, K,
-                                                   R, m.scale, page_size, m.chunk, m.window, dt, stream))
-        else:
-            check(lib.qs_hyb_latent_attention(olat.data_ptr(), qa.data_ptr(), pool.data_ptr(), _p(b.tok_slot), _p(b.tok_pos), _p(b.block_table),
-                                              b.block_table.shape[1], T, H, K, R, m.scale, page_size, m.chunk, m.window, dt, stream))
-        ov = torch.bmm(olat, self.w_uv)                                          # [H, T, Dv]
-        check(lib.qs_hyb_latent_gate_out(out.data_ptr(), out.stride(0), ov.data_ptr(), proj.data_ptr() if m.gate else None, proj.stride(0), self.col_g,
-                                         T, H, Dv, dt, stream))
+        fast = scratch is not None and LATENT_IMPL != "plain" and lib.qs_hyb_latent_attention_fast_supported(dt, H, K, R) == 1
+        # portions of at least StepBatch.TILE_MIN tokens: per-head keys and values (less arithmetic per score than the K + R numbers of a cell);
+        # single tokens and short portions: queries taken to the latent, scored against the cells as they lie
+        per_head = fast and self.per_head_ok and LATENT_IMPL != "latent" and b.n_tiles > 0 and b.n_ctx_pages > 0
+        latent = not per_head or b.n_short > 0
+        qa = olat = ov = otok = None
+        if latent:
+            qlat = torch.bmm(q.view(T, H, D + R)[:, :, :D].transpose(0, 1), self.w_uk)  # [H, T, K]
+            qa = torch.empty((T, H, K + R), dtype=proj.dtype, device=dev)
+        check(lib.qs_hyb_latent_query(_p(qa), qlat.data_ptr() if latent else None, q.data_ptr(), q.stride(0), _p(self.inv_freq), self.rot_dims,
+                                      _p(b.tok_pos), T, H, D, K, R, 1 if per_head else 0, dt, stream))
+        if per_head:
+            cells = pool.index_select(0, b.ctx_src).view(-1, K + R)
+            keys, values = torch.mm(cells, self.w_keys.t()), torch.mm(cells[:, :K], self.w_values.t())
+            otok = torch.empty((T, H * Dv), dtype=proj.dtype, device=dev)
+            check(lib.qs_hyb_attention_fast(otok.data_ptr(), otok.stride(0), q.data_ptr(), q.stride(0), keys.data_ptr(), values.data_ptr(), _p(b.tok_slot),
+                                            _p(b.tok_pos), b.ctx_table.data_ptr(), b.ctx_table.shape[1], _p(b.tile_entry), _p(b.tile_row0), b.n_tiles,
+                                            _p(b.long_tokens), b.n_long, None, 0, _p(b.entry_start), _p(b.entry_len), _p(b.entry_slot), _p(b.entry_pos0),
+                                            scratch.data_ptr(), H, H, 1, D + R, Dv, m.scale, 0.0, 1.0, self.eps, 0, page_size, m.chunk, m.window, None, dt,
+                                            stream))
+        if latent:
+            olat = torch.empty((H, T, K), dtype=proj.dtype, device=dev)
+            if fast:
+                check(lib.qs_hyb_latent_attention_fast(olat.data_ptr(), qa.data_ptr(), pool.data_ptr(), _p(b.tok_slot), _p(b.tok_pos), _p(b.block_table),
+                                                       b.block_table.shape[1], _p(b.tile_entry), _p(b.tile_row0), 0 if per_head else b.n_tiles,
+                                                       _p(b.short_tokens), b.n_short, _p(b.entry_start), _p(b.entry_len), _p(b.entry_slot),
+                                                       _p(b.entry_pos0), T, scratch.data_ptr(), H, K, R, m.scale, page_size, m.chunk, m.window, dt, stream))
+            else:
+                check(lib.qs_hyb_latent_attention(olat.data_ptr(), qa.data_ptr(), pool.data_ptr(), _p(b.tok_slot), _p(b.tok_pos), _p(b.block_table),
+                                                  b.block_table.shape[1], T, H, K, R, m.scale, page_size, m.chunk, m.window, dt, stream))
+            ov = torch.bmm(olat, self.w_uv)                                      # [H, T, Dv]
+        check(lib.qs_hyb_latent_gate_out(out.data_ptr(), out.stride(0), _p(ov), _p(otok), otok.stride(0) if per_head else 0, _p(b.tok_entry),
+                                         _p(b.entry_len), StepBatch.TILE_MIN if latent else 1, proj.data_ptr() if m.gate else None, proj.stride(0),
+                                         self.col_g, T, H, Dv, dt, stream))
 
 
-LATENT_IMPL = None  # tests: "plain" keeps the latent attention on the CUDA-core kernel
+LATENT_IMPL = None  # tests: "plain" keeps the latent attention on the CUDA-core kernel, "latent" keeps prompt portions on the latent-space tiles
 
 
 class ParallelMixer(_Mixer):

@@ -443,17 +443,20 @@ def test_far_token_is_seen(dev, far):
 
 
 def test_tensor_core_path_through_engine(dev):
-    """bfloat16 models whose latent sizes the tensor-core kernels take: whole prompts, portions, single tokens (graph replay) and a mixed batch
-    through the engine, against the oracle and against the same engine kept on the plain kernel."""
+    """bfloat16 models whose sizes the tensor-core kernels take: whole prompts, portions, single tokens (graph replay) and a mixed batch through
+    the engine, against the oracle and against the same engine kept on the plain kernel.  Prompt portions run on per-head keys and values laid
+    out from the cached rows where the head sizes allow, else (and when told so) on tiles in the latent space; single tokens always there."""
     import qserve_b200.hybrid as hyb
 
-    stack = [latent_layer(heads=4, dim=16, rot_dim=8, vdim=16, kv_rank=32, q_rank=24), latent_layer(heads=20, dim=8, rot_dim=16, vdim=8, kv_rank=64, q_rank=32, mlp=None)]
+    stack = [latent_layer(heads=4, dim=16, rot_dim=16, vdim=32, kv_rank=32, q_rank=24),           # prompt portions on per-head keys and values
+             latent_layer(heads=20, dim=8, rot_dim=16, vdim=8, kv_rank=64, q_rank=32, mlp=None),  # sizes only the latent-space tiles take
+             latent_layer(heads=3, dim=40, rot_dim=8, vdim=64, kv_rank=128, q_rank=16, mlp=None)]
     cfg = make_config(stack, loop=(0, 1, 2))
     w = make_weights(cfg, 13, sharp=2.0)
     a, b = random_tokens(200, cfg["vocab"], 13), random_tokens(90, cfg["vocab"], 14)
     wa, wb = O.forward(cfg, w, a), O.forward(cfg, w, b)
     runs = {}
-    for impl in (None, "plain"):
+    for impl in (None, "latent", "plain"):
         hyb.LATENT_IMPL = impl
         try:
             eng = _engine(cfg, w, torch.bfloat16, page_size=16)
@@ -472,8 +475,9 @@ def test_tensor_core_path_through_engine(dev):
             hyb.LATENT_IMPL = None
     for got, want in zip(runs[None], (wa, wa, wa[:190], wb)):
         assert row_err(got, want) < 0.06
-    for f, p in zip(runs[None], runs["plain"]):
-        assert row_err(f, p) < 0.03
+    for impl in (None, "latent"):
+        for f, p in zip(runs[impl], runs["plain"]):
+            assert row_err(f, p) < 0.03
 
 
 def test_generate_through_scheduler(dev):

@@ -700,7 +700,7 @@ class HybridDecoder:
             raise NotImplementedError("layer norms are built for parallel blocks with plain gains")
         self.final_norm_b = f32(weights["final.norm.b"]) if cfg.norm_kind == "layer" else None
         self.loop_in = None
-        if cfg.loop_in:
+        if cfg.loop_in and cfg.pass_starts():
             self.loop_in = st(weights["loop.in"])
             if tuple(self.loop_in.shape) != (W, 2 * W):
                 raise ValueError("loop.in must be [width, 2 width]")

@@ -115,7 +115,7 @@ def test_bias_gelu_and_softcap_kernels(dev, dtype, ff, in_stride):
 
 
 @pytest.mark.parametrize("T", [7, 700])
-@pytest.mark.parametrize("experts,top,groups,keep,width", [(6, 2, 3, 2, 48), (8, 4, 2, 1, 40), (1, 1, 1, 1, 16), (64, 6, 8, 3, 256), (12, 12, 12, 12, 33),
+@pytest.mark.parametrize("experts,top,groups,keep,width", [(6, 2, 3, 2, 48), (8, 3, 2, 1, 40), (1, 1, 1, 1, 16), (64, 6, 8, 3, 256), (12, 12, 12, 12, 33),
                                                           (40, 3, 40, 3, 64), (9, 2, 3, 1, 20), (66, 5, 2, 2, 48)])
 def test_grouped_sigmoid_router_kernel(dev, experts, top, groups, keep, width, T):
     from qserve_b200._lib import check, lib
@@ -168,7 +168,7 @@ def _latent_case(dev, dtype, H, K, R, lens, page=16, seed=0, needle=None):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("H,K,R", [(1, 8, 2), (3, 24, 8), (8, 64, 16), (5, 33, 0), (20, 40, 6), (2, 512, 64), (16, 128, 32), (9, 100, 4)])
+@pytest.mark.parametrize("H,K,R", [(1, 8, 2), (3, 24, 8), (8, 64, 8), (5, 33, 0), (20, 40, 6), (2, 512, 64), (16, 128, 32), (9, 100, 4)])
 def test_latent_attention_kernel(dev, dtype, H, K, R):
     """The plain kernel against the direct sum: several sequences in one launch, pages out of order, prompts and single tokens, lengths at and
     around page and tile borders."""
@@ -205,7 +205,7 @@ def test_latent_attention_far_key(dev, dtype, key):
         assert _rows_rel(out, want) < (2e-5 if dtype == torch.float32 else 2.0 ** -7)
 
 
-@pytest.mark.parametrize("H,K,R", [(1, 32, 8), (8, 64, 16), (16, 128, 0), (20, 64, 24), (40, 256, 32), (128, 64, 8), (16, 512, 64), (3, 32, 40)])
+@pytest.mark.parametrize("H,K,R", [(1, 32, 8), (8, 64, 40), (16, 128, 0), (20, 64, 24), (40, 256, 32), (128, 64, 8), (16, 512, 64), (3, 32, 40)])
 def test_latent_attention_tensor_core_kernel(dev, H, K, R):
     """The tensor-core kernels (rows of a tile = (token, head) pairs; single tokens with their cells shared out over blocks) against the direct
     sum and against the plain kernel: long portions, short ones, single tokens, at page and tile borders, all in one launch."""
@@ -290,7 +290,7 @@ def test_single_latent_layer(dev, layer):
 
 
 @pytest.mark.parametrize("spec", [dense(), dense(ff=1), dense(ff=300), moe(), moe(experts=1, top=1, ff=8, groups=1, keep=1),
-                                  moe(experts=8, top=4, ff=16, groups=2, keep=1), moe(experts=9, top=9, ff=5, groups=9, keep=9),
+                                  moe(experts=8, top=3, ff=16, groups=2, keep=1), moe(experts=9, top=9, ff=5, groups=9, keep=9),
                                   moe(experts=36, top=3, ff=24, groups=6, keep=2)],
                          ids=lambda s: s["kind"] + "-" + "-".join(str(v) for v in (s.get("router") or s).values() if isinstance(v, int)))
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])

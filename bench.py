@@ -65,6 +65,10 @@ def parse():
                     "(latent attention over a cache of latent rows, one layer norm per parallel block, dense and grouped-sigmoid expert "
                     "feed-forwards, loop input projection; random weights) at layer sizes of real models, beside the Rizurax hybrid decoder at "
                     "equal size; prints one JSON line")
+    ap.add_argument("--zuzezen", action="store_true", help="instead of the default workload: prefill and decode throughput of the Zuzezen decoder "
+                    "(post-norm blocks, gated linear attention, windowed attention with tied values and a distance bias, latent attention with a "
+                    "sink; random weights) at layer sizes of real models, beside the Rizurax hybrid decoder at equal size and its like kernels "
+                    "in the other designs; prints one JSON line")
     return ap.parse_args()
 
 
@@ -1045,7 +1049,7 @@ def nusuvik_block(args):
                                                        b_.block_table.data_ptr(), b_.block_table.shape[1], b_.tile_entry.data_ptr(), b_.tile_row0.data_ptr(),
                                                        b_.n_tiles, b_.short_tokens.data_ptr(), b_.n_short, b_.entry_start.data_ptr(), b_.entry_len.data_ptr(),
                                                        b_.entry_slot.data_ptr(), b_.entry_pos0.data_ptr(), n, scratch.data_ptr(), H, KR, R, lat.scale, 64, 0, 0,
-                                                       0, raw()))
+                                                       None, 0, raw()))
                 return 1
             ta = time_kernel(lambda: attn(pb, T), reps, stream)
             kern["latent_tile_kernel_prefill"] = {"us": ta * 1e6, "useful_tflops": useful / ta / 1e12, "executed_tflops": executed / ta / 1e12,
@@ -1062,7 +1066,7 @@ def nusuvik_block(args):
             def attn_long():
                 check(lib.qs_hyb_latent_attention_fast(ol.data_ptr(), qa.data_ptr(), big.data_ptr(), lb.tok_slot.data_ptr(), lb.tok_pos.data_ptr(),
                                                        lt.data_ptr(), lt.shape[1], None, None, 0, lb.short_tokens.data_ptr(), lb.n_short, None, None, None,
-                                                       None, B, scratch.data_ptr(), H, KR, R, lat.scale, 64, 0, 0, 0, raw()))
+                                                       None, B, scratch.data_ptr(), H, KR, R, lat.scale, 64, 0, 0, None, 0, raw()))
                 return 1
             ta = time_kernel(attn_long, reps * 2, stream)
             kern[f"latent_tile_kernel_decode(+merge), context {LONG}"] = {"us": ta * 1e6, "frac_of_measured_hbm": B * LONG * (KR + R) * 2 / ta / 1e9 / hbm_gbs}
@@ -1134,6 +1138,174 @@ def nusuvik_block(args):
 
 
 # ------------------------------------------------------------------------------------------------------------
+# --zuzezen: the Zuzezen decoder beside the closest existing model (the Rizurax hybrid decoder) at equal size
+# ------------------------------------------------------------------------------------------------------------
+def zuzezen_block(args):
+    """Prefill (4 prompts x 2048 tokens in one step) and decode (64 sequences at 1024 tokens of context) of a five-layer Zuzezen stack gla |
+    latent attention | attention | latent attention | gla (the attention layers with a feed-forward) beside a four-layer Rizurax stack at equal
+    width, head geometry and feed-forward size; then each Zuzezen kernel beside its like kernel of another design at equal size: the
+    windowed attention (window 1024, 4 kept positions, distance bias, head gate, tied values) beside one-map sink attention whose chunk
+    spans the same keys, the gated-linear scan beside the gate recurrence on the same scan kernel, latent attention with a sink and direct
+    queries beside the one with a query latent, the post-norm landing kernel beside the add + norm kernel, the biased silu gate beside the
+    gelu gate."""
+    import torch
+
+    from qserve_b200._lib import check, lib
+    from qserve_b200.engine import Engine
+    from qserve_b200.hybrid import MIXERS, HybridDecoder, StepBatch, random_weights
+    from qserve_b200.modelcfg import (AttentionMixerConfig, DeltaMixerConfig, GatedLinearMixerConfig, GateRecurrenceMixerConfig, HybridConfig,
+                                      HybridLayerConfig, LatentAttentionMixerConfig, MlpConfig, RotaryConfig)
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    hbm_gbs = peaks()[0]
+    try:
+        tflops = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops"]
+    except (OSError, KeyError, ValueError):
+        tflops = 1590.0
+    stream = torch.cuda.current_stream()
+    reps = max(3, args.kernel_reps)
+    raw = lambda: torch._C._cuda_getCurrentRawStream(0)
+    B, CTX, NP, LP, KR, R, WIN, KEEP = 64, 1024, 4, 2048, 512, 64, 1024, 4
+    out = {"metric": "Zuzezen decoder throughput (tokens/s, random weights, bf16, 5 layers)", "unit": "tokens/s", "impl": "ours",
+           "dtype": "bf16", "data": "synthetic", "peaks": {"hbm_gbs": hbm_gbs, "bf16_tflops": tflops}, "sizes": {}}
+
+    def steps(model, eng, V, g):
+        prompts = [torch.randint(0, V, (LP,), generator=g).tolist() for _ in range(NP)]
+        for i, p_ in enumerate(prompts):
+            eng.cache.admit(("p", i)); eng.cache.reserve(("p", i), LP)
+        pb = StepBatch.build([(eng.cache.seqs[("p", i)].slot, 0, -1, p_) for i, p_ in enumerate(prompts)], eng.cache.sync_block_table(), dev,
+                             eng.cache.page_size)
+        t = time_kernel(lambda: (model.forward(pb, eng.cache), 1)[1], reps, stream)
+        rec = {"prefill": {"tokens": NP * LP, "ms": t * 1e3, "tokens_per_s": NP * LP / t}}
+        for i in range(B):
+            eng.cache.admit(("d", i)); eng.cache.reserve(("d", i), CTX + 1)
+        db = StepBatch.build([(eng.cache.seqs[("d", i)].slot, CTX, 5, [int(torch.randint(0, V, (1,), generator=g))]) for i in range(B)],
+                             eng.cache.sync_block_table(), dev)
+        t = time_kernel(lambda: (model.logits(model.forward(db, eng.cache)), 1)[1], reps * 4, stream)
+        rec["decode"] = {"batch": B, "ctx": CTX, "ms": t * 1e3, "tokens_per_s": B / t}
+        return rec, pb, db
+
+    def mixer_times(mixer, run_cache, pb, db, T):
+        proj = torch.randn(T, mixer.in_features, device=dev).to(torch.bfloat16)
+        cat = torch.empty(T, mixer.out_features, dtype=torch.bfloat16, device=dev)
+        scratch = torch.empty(max(1, mixer.scratch_floats(T)), dtype=torch.float32, device=dev)
+        tp = time_kernel(lambda: (mixer.run(proj, cat, pb, run_cache, 64, scratch, 0, raw()), 1)[1], reps, stream)
+        td = time_kernel(lambda: (mixer.run(proj[:B], cat[:B], db, run_cache, 64, scratch, 0, raw()), 1)[1], reps * 4, stream)
+        return tp, td
+
+    def lone_mixer(mcfg, W, seed):
+        """A mixer of another design with random weights, and storage for it in a cache of its own."""
+        c1 = HybridConfig("bench", 8, W, 1e-5, (HybridLayerConfig("m", mcfg, None),))
+        w = {k[len("l0.mix."):]: v for k, v in random_weights(c1, seed, dev).items() if k.startswith("l0.mix.")}
+        return MIXERS[type(mcfg)](mcfg, w, 1e-5, torch.bfloat16, dev)
+
+    for name, (W, H, G, D, FF, V) in HYBRID_SIZES.items():
+        T = NP * LP
+        gla = GatedLinearMixerConfig(H, D, D, 8.0, 32)
+        lat = LatentAttentionMixerConfig(H, D, R, D, KR, 0, RotaryConfig(R, 1e6, 4.0, 4096, 32.0, 1.0), (D + R) ** -0.5, gate=True, gate_wide=True, sink=True)
+        att = AttentionMixerConfig(H, G, D, D, None, D ** -0.5, bias=True, qk_norm=True, window=WIN, keep_first=KEEP, qk_gain=True, tied_values=True,
+                                   distance_slope=8.0, head_gate=True)
+        ffc = MlpConfig("dense", FF, gated=True, bias=True, act="silu")
+        cfg = HybridConfig("Zuzezen", V, W, 1e-5, tuple(HybridLayerConfig(t, m, f) for t, m, f in
+                                                        (("gla", gla, None), ("latent_attention", lat, ffc), ("attention", att, ffc),
+                                                         ("latent_attention", lat, ffc), ("gla", gla, None))),
+                           norm_offset=1.0, block="post", embed_scale=8.0, layer_scale=True)
+        g = torch.Generator().manual_seed(0)
+        with torch.no_grad():
+            model = HybridDecoder(cfg, random_weights(cfg, 0, dev), torch.bfloat16, dev)
+            eng = Engine(model, max_tokens=B * (CTX + 64) + NP * LP, max_seqs=B + NP)
+            rec, pb, db = steps(model, eng, V, g)
+            kern = {}
+            # keys a query sees: the window (or all earlier positions while the prompt is shorter), and the kept first positions
+            pairs_win = NP * sum(min(i + 1, WIN) + (min(KEEP, i + 1 - WIN) if i + 1 > WIN else 0) for i in range(LP))
+            pairs_all = NP * (LP * (LP + 1) // 2)
+            seen_dec = min(CTX + 1, WIN) + (min(KEEP, CTX + 1 - WIN) if CTX + 1 > WIN else 0)
+            tp, td = mixer_times(model.layers[2].mixer, eng.cache.runs[2], pb, db, T)
+            kern["window_attention_prefill(bias+unit rms+gains+append, tiles with window / kept positions / distance bias, head gate)"] = {
+                "us": tp * 1e6, "tflops": H * pairs_win * 4 * D / tp / 1e12, "frac_of_measured_bf16_peak": H * pairs_win * 4 * D / tp / 1e12 / tflops}
+            kern["window_attention_decode(the same, head groups)"] = {"us": td * 1e6, "frac_of_measured_hbm": B * seen_dec * G * 2 * D * 2 / td / 1e9 / hbm_gbs}
+            tp, td = mixer_times(model.layers[0].mixer, eng.cache.runs[0], pb, db, T)
+            state_bytes = B * H * D * D * 4 * 2
+            kern["gated_linear_prefill(decay product+prepare+scan+norm and gate)"] = {"us": tp * 1e6, "tokens_per_s": T / tp,
+                                                                                      "state_updates_gflops": T * H * D * D * 4 / tp / 1e9}
+            kern["gated_linear_decode(the same)"] = {"us": td * 1e6, "state_frac_of_measured_hbm": state_bytes / td / 1e9 / hbm_gbs}
+            tp, td = mixer_times(model.layers[1].mixer, eng.cache.runs[1], pb, db, T)
+            useful = H * pairs_all * 2 * (D + R + D)
+            kern["latent_attention_prefill(norm+rotate+append+keys and values of every head+per-head tile attention with sink+wide gate)"] = {
+                "us": tp * 1e6, "tflops": useful / tp / 1e12, "frac_of_measured_bf16_peak": useful / tp / 1e12 / tflops}
+            kern["latent_attention_decode(norm+rotate+append+key up+latent tiles with sink+value up+wide gate)"] = {
+                "us": td * 1e6, "frac_of_measured_hbm": B * (CTX + 1) * (KR + R) * 2 / td / 1e9 / hbm_gbs}
+            ly = model.layers[1]
+            x = torch.randn(T, W, device=dev)
+            y = torch.randn(T, W, device=dev)
+            h1 = torch.empty(T, W, dtype=torch.bfloat16, device=dev)
+            tn = time_kernel(lambda: (check(lib.qs_hyb_post_norm_update(h1.data_ptr(), x.data_ptr(), y.data_ptr(), 1, ly.ff.out_bias.data_ptr(), ly.norm2.data_ptr(),
+                                                                         ly.ls2.data_ptr(), 1.0, 1e-5, T, W, 0, raw())), 1)[1], reps, stream)
+            kern["post_norm_update(fp32 rows in, bias, norm, layer scale, residual, bf16 copy)"] = {"us": tn * 1e6, "frac_of_measured_hbm": T * W * 14 / tn / 1e9 / hbm_gbs}
+            gu = torch.randn(T, 2 * FF, device=dev).to(torch.bfloat16)
+            cat = torch.empty(T, FF, dtype=torch.bfloat16, device=dev)
+            tg = time_kernel(lambda: (check(lib.qs_hyb_bias_gated_act(cat.data_ptr(), FF, gu.data_ptr(), 2 * FF, ly.ff.in_bias.data_ptr(), T, FF, 1, 0, raw())), 1)[1],
+                             reps, stream)
+            kern["bias_silu_mul"] = {"us": tg * 1e6, "frac_of_measured_hbm": T * FF * 6 / tg / 1e9 / hbm_gbs}
+            # ---- like kernels of the other designs at equal size, on this engine's batches
+            like = {}
+            sink_att = lone_mixer(AttentionMixerConfig(H, G, D, D, None, D ** -0.5, bias=True, qk_norm=True, head_temp=True, sink=True, chunk=WIN), W, 1)
+            store = eng.cache.mixer_storage(sink_att.m)
+            tp, td = mixer_times(sink_att, store, pb, db, T)
+            pairs_chunk = NP * sum(i % WIN + 1 for i in range(LP))
+            like["sink_attention_prefill(one map, chunks of the window's size)"] = {
+                "us": tp * 1e6, "tflops": H * pairs_chunk * 4 * D / tp / 1e12, "frac_of_measured_bf16_peak": H * pairs_chunk * 4 * D / tp / 1e12 / tflops}
+            like["sink_attention_decode"] = {"us": td * 1e6, "frac_of_measured_hbm": B * (CTX % WIN + 1) * G * 2 * D * 2 / td / 1e9 / hbm_gbs}
+            del store
+            full_att = lone_mixer(AttentionMixerConfig(H, G, D, D, None, D ** -0.5, bias=True, qk_norm=True, head_temp=True, sink=True), W, 1)
+            store = eng.cache.mixer_storage(full_att.m)
+            tp, td = mixer_times(full_att, store, pb, db, T)
+            like["sink_attention_prefill(one map, no mask)"] = {
+                "us": tp * 1e6, "tflops": H * pairs_all * 4 * D / tp / 1e12, "frac_of_measured_bf16_peak": H * pairs_all * 4 * D / tp / 1e12 / tflops}
+            like["sink_attention_decode(no mask)"] = {"us": td * 1e6, "frac_of_measured_hbm": B * (CTX + 1) * G * 2 * D * 2 / td / 1e9 / hbm_gbs}
+            del store
+            gate = lone_mixer(GateRecurrenceMixerConfig(H, D, D), W, 2)
+            store = eng.cache.mixer_storage(gate.m)
+            tp, td = mixer_times(gate, store, pb, db, T)
+            like["gate_recurrence_prefill(prepare+scan+norm)"] = {"us": tp * 1e6, "tokens_per_s": T / tp, "state_updates_gflops": T * H * D * D * 4 / tp / 1e9}
+            like["gate_recurrence_decode"] = {"us": td * 1e6, "state_frac_of_measured_hbm": state_bytes / td / 1e9 / hbm_gbs}
+            del store
+            qlat = lone_mixer(LatentAttentionMixerConfig(H, D, R, D, KR, 3 * W // 4, RotaryConfig(R, 1e6, layout="half"), (D + R) ** -0.5), W, 3)
+            store = eng.cache.mixer_storage(qlat.m)
+            tp, td = mixer_times(qlat, store, pb, db, T)
+            like["latent_attention_prefill(query latent, no sink, head gate)"] = {
+                "us": tp * 1e6, "tflops": useful / tp / 1e12, "frac_of_measured_bf16_peak": useful / tp / 1e12 / tflops}
+            like["latent_attention_decode(query latent, no sink, head gate)"] = {"us": td * 1e6, "frac_of_measured_hbm": B * (CTX + 1) * (KR + R) * 2 / td / 1e9 / hbm_gbs}
+            del store
+            h2 = torch.empty(T, W, dtype=torch.bfloat16, device=dev)
+            upd = torch.zeros(T, W, dtype=torch.bfloat16, device=dev)
+            tn = time_kernel(lambda: (check(lib.qs_hyb_rms_norm(h1.data_ptr(), h2.data_ptr(), x.data_ptr(), upd.data_ptr(), ly.norm1.data_ptr(),
+                                                                 ly.norm2.data_ptr(), 1.0, 1e-5, T, W, 0, raw())), 1)[1], reps, stream)
+            like["add_rms_norm_dual"] = {"us": tn * 1e6, "frac_of_measured_hbm": T * W * 14 / tn / 1e9 / hbm_gbs}
+            tg = time_kernel(lambda: (check(lib.qs_hyb_gelu_tanh_mul(cat.data_ptr(), cat.stride(0), gu.data_ptr(), T, FF, 0, raw())), 1)[1], reps, stream)
+            like["gelu_tanh_mul"] = {"us": tg * 1e6, "frac_of_measured_hbm": T * FF * 6 / tg / 1e9 / hbm_gbs}
+            rec["kernels"], rec["like_kernels_of_other_designs"] = kern, like
+            del eng, model, x, y, h1, h2, upd, gu, cat, sink_att, full_att, gate, qlat
+        torch.cuda.empty_cache()
+        # ---- the closest existing model at equal size: Rizurax (differential attention | gated delta rule, dense feed-forward)
+        ratt = AttentionMixerConfig(H, G, D, D, RotaryConfig(D // 2, 1e6, 4.0, 4096, 32.0, 1.0), D ** -0.5, maps=2, diff=0.5, head_norm=True)
+        rdlt = DeltaMixerConfig(H, G, D, D, 4)
+        rcfg = HybridConfig("Rizurax", V, W, 1e-5, tuple(HybridLayerConfig(t, m, MlpConfig("dense", FF)) for t, m in
+                                                        (("attention", ratt), ("delta", rdlt), ("attention", ratt), ("delta", rdlt))),
+                            pair_buckets=4093, pair_mul_prev=131, pair_mul_cur=11)
+        with torch.no_grad():
+            model = HybridDecoder(rcfg, random_weights(rcfg, 0, dev), torch.bfloat16, dev)
+            eng = Engine(model, max_tokens=B * (CTX + 64) + NP * LP, max_seqs=B + NP)
+            peer, _, _ = steps(model, eng, V, g)
+            del eng, model
+        torch.cuda.empty_cache()
+        rec["rizurax_equal_size"] = peer
+        out["sizes"][name] = rec
+    print(json.dumps(out), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------------------
 def main():
     args = parse()
     rank = int(os.environ.get("RANK", "0"))
@@ -1153,6 +1325,10 @@ def main():
     if args.nusuvik:
         if rank == 0:
             nusuvik_block(args)
+        return
+    if args.zuzezen:
+        if rank == 0:
+            zuzezen_block(args)
         return
     if args.impl == "reference-gpu":
         if rank == 0:

@@ -228,6 +228,16 @@ QS_API int qs_hyb_gelu_tanh_mul(void* out, int64_t out_stride, const void* in, i
 QS_API int qs_hyb_rope_append(void* proj, int64_t stride, const int32_t* tok_slot, const int32_t* tok_pos, const int32_t* block_table,
                               int max_blocks, void* kpool, void* vpool, const float* inv_freq, float amplitude, int tokens_n, int heads,
                               int kv_heads, int maps, int dim, int vdim, int rot_dims, int page_size, int dtype, void* stream);
+/* Optional parts of qs_hyb_attention / qs_hyb_attention_fast (a NULL pointer: none of them).
+ * keep_first: with a window (and no chunks), positions < keep_first of the sequence stay visible to every later query.
+ * slopes (fp32 [heads], may be NULL): slopes[h] * (query position - key position) is taken off head h's scaled score.
+ * gate (storage type, may be NULL): head h's output of token t is multiplied by sigmoid(gate[t * gate_stride + h]). */
+typedef struct {
+  int keep_first;
+  const float* slopes;
+  const void* gate;
+  int64_t gate_stride;
+} qs_attn_extra;
 /* causal attention of every token over positions first..tok_pos of its sequence in the paged cache, `maps` (1 or 2) softmax maps per head
  * over shared values: o = a1 [- lambda a2]; head_norm: o *= rsqrt(mean(o^2) + eps); o *= out_scale.  out [tokens, heads*vdim].
  * first = start of the position's chunk of `chunk` positions (0: no chunks; chunks count from position 0 of the sequence), and at least
@@ -236,7 +246,8 @@ QS_API int qs_hyb_rope_append(void* proj, int64_t stride, const int32_t* tok_slo
 QS_API int qs_hyb_attention(void* out, int64_t out_stride, const void* q, int64_t q_stride, const void* kpool, const void* vpool,
                             const int32_t* tok_slot, const int32_t* tok_pos, const int32_t* block_table, int max_blocks, int tokens_n,
                             int heads, int kv_heads, int maps, int dim, int vdim, float scale, float lambda, float out_scale, float eps,
-                            int head_norm, int page_size, int chunk, int window, const float* sinks, int dtype, void* stream);
+                            int head_norm, int page_size, int chunk, int window, const float* sinks, const qs_attn_extra* extra, int dtype,
+                            void* stream);
 /* The same attention on the fast kernels (bfloat16 storage, dim and vdim multiples of 16, vdim in {32, 64, 96, 128, 256}, heads / kv_heads <= 16):
  * entries of at least 16 tokens run as 64-row tiles on the tensor cores (tile_entry / tile_row0: entry and first row within it of every tile;
  * long_tokens: their token rows), the tokens listed in short_tokens one by one, the query heads of a key/value head as the rows of a
@@ -251,7 +262,7 @@ QS_API int qs_hyb_attention_fast(void* out, int64_t out_stride, const void* q, i
                                  const int32_t* short_tokens, int n_short, const int32_t* entry_start, const int32_t* entry_len,
                                  const int32_t* entry_slot, const int32_t* entry_pos0, float* scratch, int heads, int kv_heads, int maps, int dim,
                                  int vdim, float scale, float lambda, float out_scale, float eps, int head_norm, int page_size, int chunk,
-                                 int window, const float* sinks, int dtype, void* stream);
+                                 int window, const float* sinks, const qs_attn_extra* extra, int dtype, void* stream);
 /* gated delta rule over projection rows [G*dim q | G*dim k | H*vdim v | H*vdim gate | H b | H a]: short convolution (taps) + silu on
  * q | k | v, unit q (times dim^-1/2) and k, beta = sigmoid(b), decay = exp(-exp(a_log) softplus(a + dt_bias)), then per head
  * S <- decay S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q; out = o * rsqrt(mean(o^2) + eps) * norm_w * silu(gate).
@@ -277,11 +288,14 @@ QS_API int qs_hyb_branch_norm_mean(float* y, const void* a, const void* b, const
 /* Query / key preparation and cache append for one softmax map per head.  Projection rows [H*dim q | G*dim k | G*vdim v]; bias (fp32, same
  * layout) and q_factor (fp32 [H]) may be NULL.  Per head: + bias; (unit_rms) x *= rsqrt(mean(x^2) + eps); rotary on the first rot_dims
  * entries (rot_layout 0: pairs (2i, 2i+1); 1: pairs (i, i + rot_dims/2); angle = position * inv_freq[i]; rot_dims 0: none); queries times
- * q_factor[head], in place.  Keys and values (+ bias) go to the pages K [page][page_size][G][dim], V [page][page_size][G][vdim]. */
+ * q_factor[head], in place.  Keys and values (+ bias) go to the pages K [page][page_size][G][dim], V [page][page_size][G][vdim].
+ * q_gain / k_gain (fp32 [dim], may be NULL): gains of the unit-RMS heads, shared by the heads.  tied_values: the rows have no v part, a key
+ * head's value is that key head as projected (+ bias), not yet normed (vdim == dim). */
 QS_API int qs_hyb_qk_prepare_append(void* proj, int64_t stride, const float* bias, const float* q_factor, const int32_t* tok_slot,
                                     const int32_t* tok_pos, const int32_t* block_table, int max_blocks, void* kpool, void* vpool,
                                     const float* inv_freq, int rot_layout, int rot_dims, int unit_rms, float eps, int tokens_n, int heads,
-                                    int kv_heads, int dim, int vdim, int page_size, int dtype, void* stream);
+                                    int kv_heads, int dim, int vdim, int page_size, const float* q_gain, const float* k_gain, int tied_values,
+                                    int dtype, void* stream);
 /* Gate recurrence (HGRN2) over projection rows [H*dim q | H*dim f | H*vdim v]: q <- silu(q), f <- lower + (1 - lower) sigmoid(f + f_bias)
  * (fp32 [H*dim] each), per head S <- diag(f) S + (1 - f) v^T, o = S^T q, out = o rsqrt(mean(o^2) + eps) norm_w (fp32 [vdim], may be NULL).
  * state fp32 [slots, H, dim, vdim]; a run that starts at position 0 starts from zero.  prep fp32 [tokens, 2 H dim + H vdim] and o_raw fp32
@@ -297,6 +311,14 @@ QS_API int qs_hyb_retention(void* out, int64_t out_stride, float* prep, float* o
                             const float* inv_freq, int rot_dims, float k_scale, int gated, float* state, const int32_t* tok_pos,
                             const int32_t* entry_start, const int32_t* entry_len, const int32_t* entry_slot, const int32_t* entry_pos0,
                             int tokens_n, int entries, int heads, int dim, int vdim, float eps, int dtype, void* stream);
+/* Gated linear attention over projection rows [H*dim q | H*dim k | H*vdim v | H*vdim gate | ...] and decay logits z fp32 [tokens, H*dim]
+ * (+ z_bias fp32 [H*dim], may be NULL): q times dim^-1/2, a = sigmoid(z)^(1/tau) per head and row, per head S <- diag(a) S + k v^T, o = S^T q,
+ * out = o rsqrt(mean(o^2) + eps) norm_w (fp32 [vdim], may be NULL) silu(gate).  state fp32 [slots, H, dim, vdim]; a run that starts at position 0
+ * starts from zero.  prep fp32 [tokens, 3 H dim + H vdim] and o_raw fp32 [tokens, H vdim] are scratch. */
+QS_API int qs_hyb_gated_linear(void* out, int64_t out_stride, float* prep, float* o_raw, const void* proj, int64_t stride, const float* z,
+                               const float* z_bias, float tau, const float* norm_w, float* state, const int32_t* entry_start,
+                               const int32_t* entry_len, const int32_t* entry_slot, const int32_t* entry_pos0, int tokens_n, int entries, int heads,
+                               int dim, int vdim, float eps, int dtype, void* stream);
 /* Mixture-of-experts router: fp32 logits z = w_router [experts, width] h.  route fp32 [tokens, experts] (weight of a chosen expert, 0
  * elsewhere), top_idx int32 / top_w fp32 [tokens, top], best first (ties: the lower index).
  * QS_ROUTER_SOFTMAX: scores softmax(z) over all experts, the `top` largest kept as they are (correction, groups, keep unused).
@@ -335,6 +357,17 @@ QS_API int qs_hyb_stream_update_norm(void* out_h, void* cat_out, float* x, const
 /* out[t, i] = gelu_tanh(in[t, i] + bias[i]) (bias fp32, may be NULL); rows of in_stride / out_stride elements */
 QS_API int qs_hyb_bias_gelu_tanh(void* out, int64_t out_stride, const void* in, int64_t in_stride, const float* bias, int tokens_n, int ff,
                                  int dtype, void* stream);
+/* Post-norm residual update: y = add (+ add_bias, fp32 [width], may be NULL); x <- x + y rsqrt(mean(y^2) + eps) (offset + w) (* ls, fp32
+ * [width], may be NULL); out_h (may be NULL) <- x in the storage type.  add rows: fp32 if add_f32, else storage type; x fp32 [tokens, width]. */
+QS_API int qs_hyb_post_norm_update(void* out_h, float* x, const void* add, int add_f32, const float* add_bias, const float* w, const float* ls,
+                                   float offset, float eps, int tokens_n, int width, int dtype, void* stream);
+/* out[i] = x[i] in the storage type (x fp32) */
+QS_API int qs_hyb_cast_rows(void* out, const float* x, int64_t n, int dtype, void* stream);
+/* out[t, i] = act(in[t, i] + bias[i]) * (in[t, ff + i] + bias[ff + i]) (bias fp32 [2 ff], may be NULL); rows of in_stride / out_stride elements */
+#define QS_ACT_GELU_TANH 0
+#define QS_ACT_SILU 1
+QS_API int qs_hyb_bias_gated_act(void* out, int64_t out_stride, const void* in, int64_t in_stride, const float* bias, int tokens_n, int ff, int act,
+                                 int dtype, void* stream);
 /* x[i] <- cap tanh(x[i] / cap), fp32 in place */
 QS_API int qs_hyb_softcap(float* x, int64_t n, float cap, void* stream);
 
@@ -342,21 +375,24 @@ QS_API int qs_hyb_softcap(float* x, int64_t n, float cap, void* stream);
  * key part shared by all heads: pool [page][page_size][kv_rank + rot_dim].
  * qs_hyb_latent_prepare: from the rows of the first projection (query latent at column col_q, q_rank wide; key/value latent and rotated part
  * at col_kv, kv_rank + rot_dim wide): cq [tokens, q_rank] = unit-RMS query latent times gain_q; the token's cell = [unit-RMS latent times
- * gain_kv | rotated part].  Rotation: entry i < rot_dims/2 pairs with entry i + rot_dims/2, angle = position * inv_freq[i]. */
+ * gain_kv | rotated part].  Rotation: rot_layout 1 pairs entry i < rot_dims/2 with entry i + rot_dims/2, rot_layout 0 pairs entries
+ * (2i, 2i + 1); angle = position * inv_freq[i], cos and sin times `amplitude`.  q_rank 0: there is no query latent (cq, gain_q may be NULL). */
 QS_API int qs_hyb_latent_prepare(void* cq, const void* proj, int64_t stride, int col_q, int col_kv, const float* gain_q, const float* gain_kv,
                                  const float* inv_freq, int rot_dims, const int32_t* tok_slot, const int32_t* tok_pos,
                                  const int32_t* block_table, int max_blocks, void* pool, int tokens_n, int q_rank, int kv_rank, int rot_dim,
-                                 int page_size, float eps, int dtype, void* stream);
+                                 int page_size, float eps, int rot_layout, float amplitude, int dtype, void* stream);
 /* qa [tokens, heads, kv_rank + rot_dim] = [qlat[head, token, :] | rotated q[token, head * (dim + rot_dim) + dim ...]]: the queries as they are
  * scored against the cells (qlat [heads, tokens, kv_rank]: the unrotated query parts taken through the heads' key up-projections).  qa may be
  * NULL.  rotate_back: the rotated part also replaces q's own. */
 QS_API int qs_hyb_latent_query(void* qa, const void* qlat, void* q, int64_t q_stride, const float* inv_freq, int rot_dims, const int32_t* tok_pos,
-                               int tokens_n, int heads, int dim, int kv_rank, int rot_dim, int rotate_back, int dtype, void* stream);
+                               int tokens_n, int heads, int dim, int kv_rank, int rot_dim, int rotate_back, int rot_layout, float amplitude, int dtype,
+                               void* stream);
 /* out [heads, tokens, kv_rank] = softmax-weighted sum of the cells' first kv_rank numbers over positions first..tok_pos (first as in
- * qs_hyb_attention), scores scale * qa . cell in fp32.  Any shape with kv_rank <= 512. */
+ * qs_hyb_attention), scores scale * qa . cell in fp32.  Any shape with kv_rank <= 512.  sinks (fp32 [heads], may be NULL): one more term
+ * exp(sinks[head]) in the head's softmax denominators, without a value and outside `scale`. */
 QS_API int qs_hyb_latent_attention(void* out, const void* qa, const void* pool, const int32_t* tok_slot, const int32_t* tok_pos,
                                    const int32_t* block_table, int max_blocks, int tokens_n, int heads, int kv_rank, int rot_dim, float scale,
-                                   int page_size, int chunk, int window, int dtype, void* stream);
+                                   int page_size, int chunk, int window, const float* sinks, int dtype, void* stream);
 /* The same on the tensor cores where qs_hyb_latent_attention_fast_supported returns 1 (bfloat16 storage, kv_rank in {32, 64, 128, 256, 512},
  * kv_rank + rot_dim a multiple of 8): the 64 rows of a tile are (token, head) pairs of one sequence.  Entries of at least 16 tokens run by the
  * tile tables of the batch (tile_entry / tile_row0: entry and first row of every span of 64 tokens), the tokens listed in short_tokens one
@@ -368,12 +404,12 @@ QS_API int qs_hyb_latent_attention_fast(void* out, const void* qa, const void* p
                                         int n_tiles, const int32_t* short_tokens, int n_short, const int32_t* entry_start,
                                         const int32_t* entry_len, const int32_t* entry_slot, const int32_t* entry_pos0, int tokens_n,
                                         float* scratch, int heads, int kv_rank, int rot_dim, float scale, int page_size, int chunk, int window,
-                                        int dtype, void* stream);
-/* out[t, h * vdim + j] = o * sigmoid(gate[t, col_g + h]) (gate may be NULL: no gate); o = ov[h, t, j] (ov [heads, tokens, vdim]) or, for tokens
+                                        const float* sinks, int dtype, void* stream);
+/* out[t, h * vdim + j] = o * sigmoid(gate[t, col_g + h]) (gate may be NULL: no gate; gate_wide: gate[t, col_g + h * vdim + j]); o = ov[h, t, j] (ov [heads, tokens, vdim]) or, for tokens
  * of entries of at least min_long tokens when alt is given, alt[t, h * vdim + j] */
 QS_API int qs_hyb_latent_gate_out(void* out, int64_t out_stride, const void* ov, const void* alt, int64_t alt_stride, const int32_t* tok_entry,
                                   const int32_t* entry_len, int min_long, const void* gate, int64_t gate_stride, int col_g, int tokens_n, int heads,
-                                  int vdim, int dtype, void* stream);
+                                  int vdim, int gate_wide, int dtype, void* stream);
 
 #ifdef __cplusplus
 }

@@ -56,16 +56,20 @@ SIGNATURES = {
     "qs_hyb_residual_add": (c_int, [_P, _P, _L, _I, _P]),
     "qs_hyb_gelu_tanh_mul": (c_int, [_P, _L, _P, _I, _I, _I, _P]),
     "qs_hyb_rope_append": (c_int, [_P, _L, _P, _P, _P, _I, _P, _P, _P, _F, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P]),
-    "qs_hyb_attention": (c_int, [_P, _L, _P, _L, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _F, _F, _F, _I, _I, _I, _I, _P, _I, _P]),
+    "qs_hyb_attention": (c_int, [_P, _L, _P, _L, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _F, _F, _F, _I, _I, _I, _I, _P, _P, _I, _P]),
     "qs_hyb_attention_fast_supported": (c_int, [_I, _I, _I, _I, _I, _I, _L]),
     "qs_hyb_attention_scratch_floats": (_L, [_I, _I, _I, _I, _I]),
     "qs_hyb_attention_fast": (c_int, [_P, _L, _P, _L, _P, _P, _P, _P, _P, _I, _P, _P, _I, _P, _I, _P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I,
-                                      _F, _F, _F, _F, _I, _I, _I, _I, _P, _I, _P]),
+                                      _F, _F, _F, _F, _I, _I, _I, _I, _P, _P, _I, _P]),
     "qs_hyb_gated_delta": (c_int, [_P, _L, _P, _P, _P, _L, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _F, _I, _P]),
     # csrc/hybrid_blocks.cu, csrc/hybrid_linear.cu
     "qs_hyb_stream_norm": (c_int, [_P, _P, _P, _I, _P, _I, _P, _P, _P, _P, _I, _F, _F, _I, _I, _I, _P]),
     "qs_hyb_branch_norm_mean": (c_int, [_P, _P, _P, _P, _P, _F, _F, _I, _I, _I, _P]),
-    "qs_hyb_qk_prepare_append": (c_int, [_P, _L, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _F, _I, _I, _I, _I, _I, _I, _I, _P]),
+    "qs_hyb_qk_prepare_append": (c_int, [_P, _L, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _F, _I, _I, _I, _I, _I, _I, _P, _P, _I, _I, _P]),
+    "qs_hyb_gated_linear": (c_int, [_P, _L, _P, _P, _P, _L, _P, _P, _F, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P]),
+    "qs_hyb_post_norm_update": (c_int, [_P, _P, _P, _I, _P, _P, _P, _F, _F, _I, _I, _I, _P]),
+    "qs_hyb_cast_rows": (c_int, [_P, _P, _L, _I, _P]),
+    "qs_hyb_bias_gated_act": (c_int, [_P, _L, _P, _L, _P, _I, _I, _I, _I, _P]),
     "qs_hyb_gate_recurrence": (c_int, [_P, _L, _P, _P, _P, _L, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P]),
     "qs_hyb_retention": (c_int, [_P, _L, _P, _P, _P, _L, _P, _P, _I, _F, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P]),
     "qs_hyb_moe_router": (c_int, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _I, _I, _I, _P]),
@@ -78,17 +82,22 @@ SIGNATURES = {
     "qs_hyb_bias_gelu_tanh": (c_int, [_P, _L, _P, _L, _P, _I, _I, _I, _P]),
     "qs_hyb_softcap": (c_int, [_P, _L, _F, _P]),
     # csrc/hybrid_latent.cu
-    "qs_hyb_latent_prepare": (c_int, [_P, _P, _L, _I, _I, _P, _P, _P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _F, _I, _P]),
-    "qs_hyb_latent_query": (c_int, [_P, _P, _P, _L, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _P]),
-    "qs_hyb_latent_attention": (c_int, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _I, _P]),
+    "qs_hyb_latent_prepare": (c_int, [_P, _P, _L, _I, _I, _P, _P, _P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _F, _I, _F, _I, _P]),
+    "qs_hyb_latent_query": (c_int, [_P, _P, _P, _L, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P]),
+    "qs_hyb_latent_attention": (c_int, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P, _I, _P]),
     "qs_hyb_latent_attention_fast_supported": (c_int, [_I, _I, _I, _I]),
     "qs_hyb_latent_attention_scratch_floats": (_L, [_I, _I, _I]),
-    "qs_hyb_latent_attention_fast": (c_int, [_P, _P, _P, _P, _P, _P, _I, _P, _P, _I, _P, _I, _P, _P, _P, _P, _I, _P, _I, _I, _I, _F, _I, _I, _I, _I,
+    "qs_hyb_latent_attention_fast": (c_int, [_P, _P, _P, _P, _P, _P, _I, _P, _P, _I, _P, _I, _P, _P, _P, _P, _I, _P, _I, _I, _I, _F, _I, _I, _I, _P, _I,
                                              _P]),
-    "qs_hyb_latent_gate_out": (c_int, [_P, _L, _P, _P, _L, _P, _P, _I, _P, _L, _I, _I, _I, _I, _I, _P]),
+    "qs_hyb_latent_gate_out": (c_int, [_P, _L, _P, _P, _L, _P, _P, _I, _P, _L, _I, _I, _I, _I, _I, _I, _P]),
 }
 
 ABI_VERSION = 1
+
+
+class AttnExtra(ctypes.Structure):
+    """qs_attn_extra: optional parts of the attention kernels (kept first positions of a window, distance-bias slopes, a sigmoid gate per head)."""
+    _fields_ = [("keep_first", c_int), ("slopes", c_void_p), ("gate", c_void_p), ("gate_stride", c_int64)]
 
 
 def _load() -> ctypes.CDLL:

@@ -15,8 +15,8 @@ from typing import Dict, List
 
 import torch
 
-from .modelcfg import (AttentionMixerConfig, DeltaMixerConfig, GateRecurrenceMixerConfig, HybridConfig, LatentAttentionMixerConfig,
-                       ParallelMixerConfig, RetentionMixerConfig)
+from .modelcfg import (AttentionMixerConfig, DeltaMixerConfig, GatedLinearMixerConfig, GateRecurrenceMixerConfig, HybridConfig,
+                       LatentAttentionMixerConfig, ParallelMixerConfig, RetentionMixerConfig)
 
 
 class OutOfPages(RuntimeError):
@@ -82,7 +82,7 @@ class HybridCache:
             c = 2 * m.kv_heads * m.dim + m.heads * m.vdim
             return {"state": torch.zeros((max_seqs, m.heads, m.dim, m.vdim), dtype=torch.float32, device=device),
                     "conv": torch.zeros((max_seqs, max(m.conv - 1, 1), c), dtype=torch.float32, device=device)}
-        if isinstance(m, (GateRecurrenceMixerConfig, RetentionMixerConfig)):
+        if isinstance(m, (GateRecurrenceMixerConfig, RetentionMixerConfig, GatedLinearMixerConfig)):
             return {"state": torch.zeros((max_seqs, m.heads, m.dim, m.vdim), dtype=torch.float32, device=device)}
         if isinstance(m, ParallelMixerConfig):
             return {"left": self.mixer_storage(m.left), "right": self.mixer_storage(m.right)}

@@ -210,7 +210,7 @@ __global__ void __launch_bounds__(kAttnThreads) paged_multimap_attention_kernel(
     ST* __restrict__ out, long long out_stride, const ST* __restrict__ q, long long q_stride, const ST* __restrict__ kpool,
     const ST* __restrict__ vpool, const int* __restrict__ tok_slot, const int* __restrict__ tok_pos, const int* __restrict__ block_table,
     int max_blocks, int H, int G, int D, int Dv, float scale, float lambda, float out_scale, float eps, int head_norm, int page, int chunk,
-    int window, const float* __restrict__ sinks) {
+    int window, const float* __restrict__ sinks, AttnExtra ex) {
   extern __shared__ float sm[];
   float* qs = sm;                      // [MAPS * D]
   float* ps = qs + MAPS * D;           // [MAPS][KT]
@@ -235,8 +235,12 @@ __global__ void __launch_bounds__(kAttnThreads) paged_multimap_attention_kernel(
     for (int j = 0; j < kAttnMaxV; ++j) acc[m][j] = 0.f;
   }
   const int n_keys = pos + 1;
-  for (int base = first_key(pos, chunk, window); base < n_keys; base += kAttnKT) {
-    const int nk = min(kAttnKT, n_keys - base);
+  const int first = first_key(pos, chunk, window), kept = min(ex.keep_first, first);
+  const float slope = ex.slopes != nullptr ? ex.slopes[h] : 0.f;
+  // two runs of keys: the kept first positions that lie before the window, then the window (or chunk, or everything) up to the token itself
+  for (int seg = kept > 0 ? 0 : 1; seg < 2; ++seg)
+  for (int base = seg == 0 ? 0 : first, hi = seg == 0 ? kept : n_keys; base < hi; base += kAttnKT) {
+    const int nk = min(kAttnKT, hi - base);
     __syncthreads();  // previous tile's ps / pages fully consumed (and qs written, first time)
     for (int j = threadIdx.x; j < nk; j += blockDim.x) pages[j] = bt[(base + j) / page];
     __syncthreads();
@@ -249,7 +253,7 @@ __global__ void __launch_bounds__(kAttnThreads) paged_multimap_attention_kernel(
         float d = 0.f;
         for (int i = lane; i < D; i += 32) d += qs[m * D + i] * ldf(kr + m * D + i);
         d = warp_sum(d);
-        if (lane == 0) ps[m * kAttnKT + j] = d * scale;
+        if (lane == 0) ps[m * kAttnKT + j] = d * scale - slope * (float)(pos - kj);
       }
     }
     __syncthreads();
@@ -311,6 +315,7 @@ __global__ void __launch_bounds__(kAttnThreads) paged_multimap_attention_kernel(
     ss = block_sum(ss, red);
     r *= 1.f / sqrtf(ss / (float)Dv + eps);
   }
+  if (ex.gate != nullptr) r *= sigmoid_f(ldf(static_cast<const ST*>(ex.gate) + (size_t)t * ex.gate_stride + h));
   ST* orow = out + (size_t)t * out_stride + (size_t)h * Dv;
 #pragma unroll
   for (int j = 0; j < kAttnMaxV; ++j) {
@@ -334,7 +339,7 @@ __global__ void __launch_bounds__(128, KT == 32 ? 3 : 2) tile_attention_kernel(
     const __nv_bfloat16* __restrict__ vpool, const int* __restrict__ tile_entry, const int* __restrict__ tile_row0,
     const int* __restrict__ entry_start, const int* __restrict__ entry_len, const int* __restrict__ entry_slot, const int* __restrict__ entry_pos0,
     const int* __restrict__ block_table, int max_blocks, int H, int G, int maps, int D, float scale, int page, int chunk, int window,
-    const float* __restrict__ sinks) {
+    const float* __restrict__ sinks, int keep, const float* __restrict__ slopes) {
   extern __shared__ __align__(16) unsigned char smraw[];
   constexpr int Dv = NVT * 16;
   const int SD = D + kPad, SV = Dv + kPad;
@@ -360,6 +365,9 @@ __global__ void __launch_bounds__(128, KT == 32 ? 3 : 2) tile_attention_kernel(
   const int last_qpos = qpos0 + n_rows - 1;
   const int n_kt = last_qpos / KT + 1;
   const int kt_lo = first_key(qpos0, chunk, window) / KT;  // the tile's first row sees furthest back
+  const int n_pre = kept_tiles(first_key(qpos0, chunk, window), keep, KT), n_walk = n_pre + n_kt - kt_lo;  // kept first positions, then the rest
+  auto tile_at = [&](int i) { return i < n_pre ? i : kt_lo + i - n_pre; };
+  const float slope2 = slopes != nullptr ? slopes[h] * 1.4426950408889634f : 0.f;
   const float scale_log2 = scale * 1.4426950408889634f;
   const int qrow = warp * 16 + (lane >> 2);  // this thread's rows: qrow, qrow + 8
   const int fk[2] = {first_key(qpos0 + qrow, chunk, window), first_key(qpos0 + qrow + 8, chunk, window)};
@@ -393,19 +401,20 @@ __global__ void __launch_bounds__(128, KT == 32 ? 3 : 2) tile_attention_kernel(
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
-  load_kv(kt_lo, kt_lo & 1, cell_of(kt_lo));
-  long long cell_next = kt_lo + 1 < n_kt ? cell_of(kt_lo + 1) : -1;
-  for (int kt = kt_lo; kt < n_kt; ++kt) {
-    if (kt + 1 < n_kt) {
-      load_kv(kt + 1, (kt + 1) & 1, cell_next);
-      if (kt + 2 < n_kt) cell_next = cell_of(kt + 2);
+  load_kv(tile_at(0), 0, cell_of(tile_at(0)));
+  long long cell_next = 1 < n_walk ? cell_of(tile_at(1)) : -1;
+  for (int wi = 0; wi < n_walk; ++wi) {
+    const int kt = tile_at(wi);
+    if (wi + 1 < n_walk) {
+      load_kv(tile_at(wi + 1), (wi + 1) & 1, cell_next);
+      if (wi + 2 < n_walk) cell_next = cell_of(tile_at(wi + 2));
       asm volatile("cp.async.wait_group 1;" ::: "memory");
     } else {
       asm volatile("cp.async.wait_group 0;" ::: "memory");
     }
     __syncthreads();
-    const __nv_bfloat16* Kc = Ks + (size_t)(kt & 1) * KT * SD;
-    const __nv_bfloat16* Vc = Vs + (size_t)(kt & 1) * KT * SV;
+    const __nv_bfloat16* Kc = Ks + (size_t)(wi & 1) * KT * SD;
+    const __nv_bfloat16* Vc = Vs + (size_t)(wi & 1) * KT * SV;
     float s[KT / 8][4];
 #pragma unroll
     for (int i = 0; i < KT / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
@@ -423,15 +432,17 @@ __global__ void __launch_bounds__(128, KT == 32 ? 3 : 2) tile_attention_kernel(
     // scale, causal mask, online softmax (rows qrow and qrow + 8; a row's columns live in the 4 lanes of a quad)
     float mx[2] = {-INFINITY, -INFINITY};
     const bool diagonal = kt * KT + KT - 1 > qpos0 + warp * 16 || kt * KT < warp_fk;
+    const bool biased = slope2 != 0.f;
 #pragma unroll
     for (int nt = 0; nt < KT / 8; ++nt)
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         float v = s[nt][j] * scale_log2;
-        if (diagonal) {  // warp-uniform: only tiles that reach past this warp's first row, or start before a row's first key, need a mask
+        if (diagonal || biased) {  // warp-uniform: only tiles that reach past this warp's first row, or start before a row's first key, need a mask
           const int kpos = kt * KT + nt * 8 + (lane & 3) * 2 + (j & 1);
           const int qp = qpos0 + qrow + (j >> 1) * 8;
-          if (kpos > qp || kpos < fk[j >> 1]) v = -INFINITY;
+          if (biased) v -= slope2 * (float)(qp - kpos);
+          if (diagonal && !key_visible(kpos, qp, fk[j >> 1], keep)) v = -INFINITY;
         }
         s[nt][j] = v;
         mx[j >> 1] = fmaxf(mx[j >> 1], v);
@@ -509,7 +520,8 @@ __global__ void __launch_bounds__(128, KT == 32 ? 3 : 2) tile_attention_kernel(
 // finish a head from its per-map outputs: o = a1 [- lambda a2]; (head_norm) unit RMS; times out_scale.  One warp per (listed token, head).
 template <typename ST>
 __global__ void multimap_combine_kernel(ST* __restrict__ out, long long out_stride, const float* __restrict__ a_in, const int* __restrict__ tok_list,
-                                        int n_list, int H, int maps, int Dv, float lambda, float out_scale, float eps, int head_norm) {
+                                        int n_list, int H, int maps, int Dv, float lambda, float out_scale, float eps, int head_norm,
+                                        const ST* __restrict__ gate, long long gate_stride) {
   const int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   if (w >= n_list * H) return;
   const int t = tok_list[w / H], h = w % H;
@@ -520,7 +532,8 @@ __global__ void multimap_combine_kernel(ST* __restrict__ out, long long out_stri
     ss += v * v;
   }
   ss = warp_sum(ss);
-  const float r = head_norm ? out_scale / sqrtf(ss / (float)Dv + eps) : out_scale;
+  float r = head_norm ? out_scale / sqrtf(ss / (float)Dv + eps) : out_scale;
+  if (gate != nullptr) r *= sigmoid_f(ldf(gate + (size_t)t * gate_stride + h));
   ST* dst = out + (size_t)t * out_stride + (size_t)h * Dv;
   for (int i = lane; i < Dv; i += 32) stf(dst + i, (maps == 2 ? a[i] - lambda * a[Dv + i] : a[i]) * r);
 }
@@ -537,7 +550,8 @@ template <int NVT, int PSPLIT>
 __global__ void __launch_bounds__(128) group_attention_kernel(
     float* __restrict__ part, const __nv_bfloat16* __restrict__ q, long long q_stride, const __nv_bfloat16* __restrict__ kpool,
     const __nv_bfloat16* __restrict__ vpool, const int* __restrict__ tok_list, const int* __restrict__ tok_slot, const int* __restrict__ tok_pos,
-    const int* __restrict__ block_table, int max_blocks, int H, int G, int maps, int D, float scale, int page, int shares, int chunk, int window) {
+    const int* __restrict__ block_table, int max_blocks, int H, int G, int maps, int D, float scale, int page, int shares, int chunk, int window,
+    int keep, const float* __restrict__ slopes) {
   extern __shared__ __align__(16) unsigned char smraw[];
   constexpr int Dv = NVT * 16;
   const int SD = D + kPad, SV = Dv + kPad, R = H / G;
@@ -550,8 +564,10 @@ __global__ void __launch_bounds__(128) group_attention_kernel(
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int dch = D >> 3;
   const int first = first_key(pos, chunk, window), kt_lo = first / kTileK;
-  const int n_kt = pos / kTileK + 1, per = (n_kt - kt_lo + shares - 1) / shares;
-  const int kt0 = kt_lo + share * per, kt1 = min(n_kt, kt0 + per);
+  // the walk over tiles (kept first positions, then from the first visible key on) is shared out: walk indices [kt0, kt1) are this block's
+  const int n_pre = kept_tiles(first, keep, kTileK), n_walk = n_pre + pos / kTileK + 1 - kt_lo, per = (n_walk + shares - 1) / shares;
+  const int kt0 = share * per, kt1 = min(n_walk, kt0 + per);
+  auto tile_at = [&](int i) { return i < n_pre ? i : kt_lo + i - n_pre; };
   float* pout = part + ((((size_t)li * H + g * R) * maps + m) * shares + share) * (size_t)(2 + Dv);  // head g R + r: + r maps shares (2 + Dv)
   const size_t head_step = (size_t)maps * shares * (2 + Dv);
   if (kt0 >= kt1) {  // a share without keys weighs nothing in the merge
@@ -592,13 +608,19 @@ __global__ void __launch_bounds__(128) group_attention_kernel(
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
-  load_kv(kt0, 0, cell_of(kt0));
-  long long cell_next = kt0 + 1 < kt1 ? cell_of(kt0 + 1) : -1;
-  for (int kt = kt0; kt < kt1; ++kt) {
-    const int buf = (kt - kt0) & 1;
-    if (kt + 1 < kt1) {
-      load_kv(kt + 1, buf ^ 1, cell_next);
-      if (kt + 2 < kt1) cell_next = cell_of(kt + 2);
+  load_kv(tile_at(kt0), 0, cell_of(tile_at(kt0)));
+  long long cell_next = kt0 + 1 < kt1 ? cell_of(tile_at(kt0 + 1)) : -1;
+  float slope2[2] = {0.f, 0.f};  // of this thread's rows (heads g R + row, g R + row + 8)
+  if (slopes != nullptr) {
+#pragma unroll
+    for (int r = 0; r < 2; ++r)
+      if ((lane >> 2) + r * 8 < R) slope2[r] = slopes[g * R + (lane >> 2) + r * 8] * 1.4426950408889634f;
+  }
+  for (int wi = kt0; wi < kt1; ++wi) {
+    const int buf = (wi - kt0) & 1, kt = tile_at(wi);
+    if (wi + 1 < kt1) {
+      load_kv(tile_at(wi + 1), buf ^ 1, cell_next);
+      if (wi + 2 < kt1) cell_next = cell_of(tile_at(wi + 2));
       asm volatile("cp.async.wait_group 1;" ::: "memory");
     } else {
       asm volatile("cp.async.wait_group 0;" ::: "memory");
@@ -622,7 +644,7 @@ __global__ void __launch_bounds__(128) group_attention_kernel(
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const int kpos = kt * kTileK + warp * 16 + nt * 8 + (lane & 3) * 2 + (j & 1);
-        const float v = kpos <= pos && kpos >= first ? s[nt][j] * scale_log2 : -INFINITY;
+        const float v = key_visible(kpos, pos, first, keep) ? s[nt][j] * scale_log2 - slope2[j >> 1] * (float)(pos - kpos) : -INFINITY;
         s[nt][j] = v;
         mx[j >> 1] = fmaxf(mx[j >> 1], v);
       }
@@ -716,7 +738,7 @@ __global__ void __launch_bounds__(128) group_attention_kernel(
 template <typename ST>
 __global__ void group_merge_kernel(ST* __restrict__ out, long long out_stride, const float* __restrict__ part, const int* __restrict__ tok_list,
                                    int n_list, int H, int maps, int Dv, int shares, float lambda, float out_scale, float eps, int head_norm,
-                                   const float* __restrict__ sinks) {
+                                   const float* __restrict__ sinks, const ST* __restrict__ gate, long long gate_stride) {
   const int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   if (w >= n_list * H) return;
   const int li = w / H, h = w - li * H, t = tok_list[li];
@@ -749,7 +771,8 @@ __global__ void group_merge_kernel(ST* __restrict__ out, long long out_stride, c
 #pragma unroll
   for (int j = 0; j < 8; ++j) ss += ov[j] * ov[j];
   ss = warp_sum(ss);
-  const float r = head_norm ? out_scale / sqrtf(ss / (float)Dv + eps) : out_scale;
+  float r = head_norm ? out_scale / sqrtf(ss / (float)Dv + eps) : out_scale;
+  if (gate != nullptr) r *= sigmoid_f(ldf(gate + (size_t)t * gate_stride + h));
   ST* dst = out + (size_t)t * out_stride + (size_t)h * Dv;
 #pragma unroll
   for (int j = 0; j < 8; ++j)
@@ -1023,21 +1046,25 @@ __global__ void delta_gate_out_kernel(ST* __restrict__ out, long long out_stride
   for (int i = lane; i < Dv; i += 32) stf(dst + i, o[i] * r * norm_w[i] * silu_f(ldf(gate + i)));
 }
 
+inline AttnExtra attn_extra(const qs_attn_extra* e) {
+  return e != nullptr ? AttnExtra{e->keep_first, e->slopes, e->gate, (long long)e->gate_stride} : AttnExtra{0, nullptr, nullptr, 0};
+}
+
 template <typename ST>
 int launch_attention(void* out, long long out_stride, const void* q, long long q_stride, const void* kpool, const void* vpool, const int* tok_slot,
                      const int* tok_pos, const int* block_table, int max_blocks, int T, int H, int G, int maps, int D, int Dv, float scale,
                      float lambda, float out_scale, float eps, int head_norm, int page, int chunk, int window, const float* sinks,
-                     cudaStream_t s) {
+                     AttnExtra ex, cudaStream_t s) {
   const size_t smem = (size_t)(maps * D + maps * kAttnKT + 33) * sizeof(float);
   dim3 grid(T, H);
   if (maps == 2) {
     if (smem > 48 * 1024) cudaFuncSetAttribute(paged_multimap_attention_kernel<ST, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     paged_multimap_attention_kernel<ST, 2><<<grid, kAttnThreads, smem, s>>>((ST*)out, out_stride, (const ST*)q, q_stride, (const ST*)kpool,
-        (const ST*)vpool, tok_slot, tok_pos, block_table, max_blocks, H, G, D, Dv, scale, lambda, out_scale, eps, head_norm, page, chunk, window, sinks);
+        (const ST*)vpool, tok_slot, tok_pos, block_table, max_blocks, H, G, D, Dv, scale, lambda, out_scale, eps, head_norm, page, chunk, window, sinks, ex);
   } else {
     if (smem > 48 * 1024) cudaFuncSetAttribute(paged_multimap_attention_kernel<ST, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     paged_multimap_attention_kernel<ST, 1><<<grid, kAttnThreads, smem, s>>>((ST*)out, out_stride, (const ST*)q, q_stride, (const ST*)kpool,
-        (const ST*)vpool, tok_slot, tok_pos, block_table, max_blocks, H, G, D, Dv, scale, lambda, out_scale, eps, head_norm, page, chunk, window, sinks);
+        (const ST*)vpool, tok_slot, tok_pos, block_table, max_blocks, H, G, D, Dv, scale, lambda, out_scale, eps, head_norm, page, chunk, window, sinks, ex);
   }
   return check_cuda(cudaGetLastError(), "hyb_attention");
 }
@@ -1057,7 +1084,8 @@ constexpr int kTileKeysPrompt = 32;
 template <int NVT, int KT>
 int launch_tiles(float* scratch, const void* q, long long q_stride, const void* kpool, const void* vpool, const int* tile_entry, const int* tile_row0,
                  int n_tiles, const int* entry_start, const int* entry_len, const int* entry_slot, const int* entry_pos0, const int* block_table,
-                 int max_blocks, int H, int G, int maps, int D, float scale, int page, int chunk, int window, const float* sinks, cudaStream_t s) {
+                 int max_blocks, int H, int G, int maps, int D, float scale, int page, int chunk, int window, const float* sinks, AttnExtra ex,
+                 cudaStream_t s) {
   const size_t smem = ((size_t)(kTileQ + 2 * KT) * (D + kPad) + (size_t)2 * KT * (NVT * 16 + kPad)) * sizeof(__nv_bfloat16);
   static bool attr_set[kMaxDevices] = {};
   if (smem > 48 * 1024 && !attr_set[device_ordinal()]) {
@@ -1065,7 +1093,8 @@ int launch_tiles(float* scratch, const void* q, long long q_stride, const void* 
     attr_set[device_ordinal()] = true;
   }
   tile_attention_kernel<NVT, 3, KT><<<dim3(n_tiles, H * maps), 128, smem, s>>>(scratch, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)kpool,
-      (const __nv_bfloat16*)vpool, tile_entry, tile_row0, entry_start, entry_len, entry_slot, entry_pos0, block_table, max_blocks, H, G, maps, D, scale, page, chunk, window, sinks);
+      (const __nv_bfloat16*)vpool, tile_entry, tile_row0, entry_start, entry_len, entry_slot, entry_pos0, block_table, max_blocks, H, G, maps, D, scale, page, chunk, window, sinks,
+      ex.keep_first, ex.slopes);
   return check_cuda(cudaGetLastError(), "hyb_attention tiles");
 }
 
@@ -1080,7 +1109,7 @@ template <int NVT>
 int launch_group(void* out, long long out_stride, float* part, const void* q, long long q_stride, const void* kpool, const void* vpool,
                  const int* tok_list, int n_list, const int* tok_slot, const int* tok_pos, const int* block_table, int max_blocks, int H, int G,
                  int maps, int D, float scale, float lambda, float out_scale, float eps, int head_norm, int page, int chunk, int window,
-                 const float* sinks, cudaStream_t s) {
+                 const float* sinks, AttnExtra ex, cudaStream_t s) {
   const size_t smem = ((size_t)(16 + 2 * kTileK) * (D + kPad) + (size_t)2 * kTileK * (NVT * 16 + kPad)) * sizeof(__nv_bfloat16);
   static bool attr_set[kMaxDevices] = {};
   if (smem > 48 * 1024 && !attr_set[device_ordinal()]) {
@@ -1089,10 +1118,12 @@ int launch_group(void* out, long long out_stride, float* part, const void* q, lo
   }
   const int shares = group_shares(n_list, G, maps);
   group_attention_kernel<NVT, 3><<<dim3(n_list, G * maps, shares), 128, smem, s>>>(part, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)kpool,
-      (const __nv_bfloat16*)vpool, tok_list, tok_slot, tok_pos, block_table, max_blocks, H, G, maps, D, scale, page, shares, chunk, window);
+      (const __nv_bfloat16*)vpool, tok_list, tok_slot, tok_pos, block_table, max_blocks, H, G, maps, D, scale, page, shares, chunk, window, ex.keep_first,
+      ex.slopes);
   const int warps = n_list * H;
   group_merge_kernel<__nv_bfloat16><<<(warps + 3) / 4, 128, 0, s>>>((__nv_bfloat16*)out, out_stride, part, tok_list, n_list, H, maps, NVT * 16, shares,
-                                                                     lambda, out_scale, eps, head_norm, sinks);
+                                                                     lambda, out_scale, eps, head_norm, sinks, (const __nv_bfloat16*)ex.gate,
+                                                                     ex.gate_stride);
   return check_cuda(cudaGetLastError(), "hyb_attention single tokens");
 }
 
@@ -1226,18 +1257,20 @@ int qs_hyb_rope_append(void* proj, int64_t stride, const int32_t* tok_slot, cons
 int qs_hyb_attention(void* out, int64_t out_stride, const void* q, int64_t q_stride, const void* kpool, const void* vpool,
                      const int32_t* tok_slot, const int32_t* tok_pos, const int32_t* block_table, int max_blocks, int tokens_n, int heads,
                      int kv_heads, int maps, int dim, int vdim, float scale, float lambda, float out_scale, float eps, int head_norm,
-                     int page_size, int chunk, int window, const float* sinks, int dtype, void* stream) {
+                     int page_size, int chunk, int window, const float* sinks, const qs_attn_extra* extra, int dtype, void* stream) {
   QS_REQUIRE(out && q && kpool && vpool && tok_slot && tok_pos && block_table, "hyb_attention: null tensor");
   QS_REQUIRE(chunk >= 0 && window >= 0, "hyb_attention: negative chunk or window");
+  const AttnExtra ex = attn_extra(extra);
+  QS_REQUIRE(ex.keep_first >= 0 && (ex.keep_first == 0 || (window > 0 && chunk == 0)), "hyb_attention: kept first positions go with a window and no chunks");
   QS_REQUIRE(maps == 1 || maps == 2, "hyb_attention: 1 or 2 softmax maps per head");
   QS_REQUIRE(heads % kv_heads == 0 && vdim <= kAttnThreads * kAttnMaxV && page_size > 0, "hyb_attention: bad head geometry (vdim <= 512)");
   if (tokens_n == 0) return qs::QS_OK;
   cudaStream_t s = (cudaStream_t)stream;
   QS_DT(dtype,
         return launch_attention<__nv_bfloat16>(out, out_stride, q, q_stride, kpool, vpool, tok_slot, tok_pos, block_table, max_blocks, tokens_n,
-                                               heads, kv_heads, maps, dim, vdim, scale, lambda, out_scale, eps, head_norm, page_size, chunk, window, sinks, s),
+                                               heads, kv_heads, maps, dim, vdim, scale, lambda, out_scale, eps, head_norm, page_size, chunk, window, sinks, ex, s),
         return launch_attention<float>(out, out_stride, q, q_stride, kpool, vpool, tok_slot, tok_pos, block_table, max_blocks, tokens_n, heads,
-                                       kv_heads, maps, dim, vdim, scale, lambda, out_scale, eps, head_norm, page_size, chunk, window, sinks, s));
+                                       kv_heads, maps, dim, vdim, scale, lambda, out_scale, eps, head_norm, page_size, chunk, window, sinks, ex, s));
 }
 
 int qs_hyb_attention_fast_supported(int dtype, int heads, int kv_heads, int maps, int dim, int vdim, int64_t q_stride) {
@@ -1256,8 +1289,11 @@ int qs_hyb_attention_fast(void* out, int64_t out_stride, const void* q, int64_t 
                           const int32_t* tile_row0, int n_tiles, const int32_t* long_tokens, int n_long, const int32_t* short_tokens, int n_short,
                           const int32_t* entry_start, const int32_t* entry_len, const int32_t* entry_slot, const int32_t* entry_pos0,
                           float* scratch, int heads, int kv_heads, int maps, int dim, int vdim, float scale, float lambda, float out_scale, float eps,
-                          int head_norm, int page_size, int chunk, int window, const float* sinks, int dtype, void* stream) {
+                          int head_norm, int page_size, int chunk, int window, const float* sinks, const qs_attn_extra* extra, int dtype,
+                          void* stream) {
   QS_REQUIRE(chunk >= 0 && window >= 0, "hyb_attention_fast: negative chunk or window");
+  const AttnExtra ex = attn_extra(extra);
+  QS_REQUIRE(ex.keep_first >= 0 && (ex.keep_first == 0 || (window > 0 && chunk == 0)), "hyb_attention_fast: kept first positions go with a window and no chunks");
   QS_REQUIRE(out && q && kpool && vpool && tok_slot && tok_pos && block_table, "hyb_attention_fast: null tensor");
   QS_REQUIRE(fast_attention_supported(dtype, heads, kv_heads, maps, dim, vdim, q_stride), "hyb_attention_fast: shape not supported (use qs_hyb_attention)");
   QS_REQUIRE(n_tiles == 0 || (tile_entry && tile_row0 && long_tokens && scratch && entry_start && entry_len && entry_slot && entry_pos0),
@@ -1267,7 +1303,7 @@ int qs_hyb_attention_fast(void* out, int64_t out_stride, const void* q, int64_t 
   if (n_tiles > 0) {
     int rc = 0;
 #define QS_TILES(NVT, KT) rc = launch_tiles<NVT, KT>(scratch, q, q_stride, kpool, vpool, tile_entry, tile_row0, n_tiles, entry_start, entry_len, entry_slot, \
-                                             entry_pos0, block_table, max_blocks, heads, kv_heads, maps, dim, scale, page_size, chunk, window, sinks, s)
+                                             entry_pos0, block_table, max_blocks, heads, kv_heads, maps, dim, scale, page_size, chunk, window, sinks, ex, s)
     switch (vdim / 16) {
       case 2: QS_TILES(2, kTileKeysPrompt); break;
       case 4: QS_TILES(4, kTileKeysPrompt); break;
@@ -1279,13 +1315,13 @@ int qs_hyb_attention_fast(void* out, int64_t out_stride, const void* q, int64_t 
     if (rc) return rc;
     const int warps = n_long * heads;
     multimap_combine_kernel<__nv_bfloat16><<<(warps + 3) / 4, 128, 0, s>>>((__nv_bfloat16*)out, out_stride, scratch, long_tokens, n_long, heads, maps, vdim,
-                                                                          lambda, out_scale, eps, head_norm);
+                                                                          lambda, out_scale, eps, head_norm, (const __nv_bfloat16*)ex.gate, ex.gate_stride);
   }
   if (n_short > 0) {
     int rc = 0;
     float* part = scratch + (size_t)(n_long + n_short) * heads * maps * vdim;  // behind the per-map outputs of the tiles
 #define QS_GROUP(NVT) rc = launch_group<NVT>(out, out_stride, part, q, q_stride, kpool, vpool, short_tokens, n_short, tok_slot, tok_pos, block_table, \
-                                             max_blocks, heads, kv_heads, maps, dim, scale, lambda, out_scale, eps, head_norm, page_size, chunk, window, sinks, s)
+                                             max_blocks, heads, kv_heads, maps, dim, scale, lambda, out_scale, eps, head_norm, page_size, chunk, window, sinks, ex, s)
     switch (vdim / 16) {
       case 2: QS_GROUP(2); break;
       case 4: QS_GROUP(4); break;

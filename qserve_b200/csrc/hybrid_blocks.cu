@@ -223,8 +223,9 @@ __global__ void branch_norm_mean_vec_kernel(float* __restrict__ y, const ST* __r
 // ---------------------------------------------------------------------------------------------------------------------------------
 // Query / key preparation of an attention layer and the append to the paged cache (one softmax map per head).
 //   projection row: [H*D q | G*D k | G*Dv v];  bias (fp32, same layout) may be null
-//   per head, in this order: + bias;  (unit_rms) x <- x * rsqrt(mean(x^2) + eps);  rotary on the first rot_dims entries (layout 0: pairs
-//   (2i, 2i+1), layout 1: pairs (i, i + rot_dims/2); angle = position * inv_freq[i]);  queries times q_factor[head] (may be null)
+//   per head, in this order: + bias;  (unit_rms) x <- x * rsqrt(mean(x^2) + eps) [* q_gain or k_gain, fp32 [D] shared by the heads];  rotary
+//   on the first rot_dims entries (layout 0: pairs (2i, 2i+1), layout 1: pairs (i, i + rot_dims/2); angle = position * inv_freq[i]);  queries
+//   times q_factor[head] (may be null).  tied_values: the row has no v part, a key head's value is that key head as projected (+ bias), not yet normed.
 // grid (tokens, H + G): the first H blocks finish a query head in place, the others store a key head and its value head (+ bias) in the pages
 // K [page][page_size][G][D], V [page][page_size][G][Dv].
 // ---------------------------------------------------------------------------------------------------------------------------------
@@ -232,7 +233,8 @@ template <typename ST>
 __global__ void qk_prepare_append_kernel(ST* __restrict__ proj, long long stride, const float* __restrict__ bias, const float* __restrict__ q_factor,
                                          const int* __restrict__ tok_slot, const int* __restrict__ tok_pos, const int* __restrict__ block_table,
                                          int max_blocks, ST* __restrict__ kpool, ST* __restrict__ vpool, const float* __restrict__ inv_freq,
-                                         int rot_layout, int rot_dims, int unit_rms, float eps, int H, int G, int D, int Dv, int page) {
+                                         int rot_layout, int rot_dims, int unit_rms, float eps, int H, int G, int D, int Dv, int page,
+                                         const float* __restrict__ q_gain, const float* __restrict__ k_gain, int tied_values) {
   extern __shared__ float hs[];  // the head, D floats
   __shared__ float red[33];
   const int t = blockIdx.x, u = blockIdx.y;
@@ -262,7 +264,17 @@ __global__ void qk_prepare_append_kernel(ST* __restrict__ proj, long long stride
     dst = kpool + (cell * G + g) * (size_t)D;
     const size_t v0 = (size_t)(H + G) * D + (size_t)g * Dv;
     ST* vd = vpool + (cell * G + g) * (size_t)Dv;
-    for (int i = threadIdx.x; i < Dv; i += blockDim.x) stf(vd + i, ldf(row + v0 + i) + (bias != nullptr ? bias[v0 + i] : 0.f));
+    if (tied_values) {
+      for (int i = threadIdx.x; i < D; i += blockDim.x) stf(vd + i, hs[i]);
+    } else {
+      for (int i = threadIdx.x; i < Dv; i += blockDim.x) stf(vd + i, ldf(row + v0 + i) + (bias != nullptr ? bias[v0 + i] : 0.f));
+    }
+  }
+  const float* gain = is_q ? q_gain : k_gain;
+  if (gain != nullptr) {
+    __syncthreads();  // the values above read the head as projected
+    for (int i = threadIdx.x; i < D; i += blockDim.x) hs[i] *= gain[i];
+    __syncthreads();
   }
   const int half = rot_dims >> 1;
   for (int i = threadIdx.x; i < D; i += blockDim.x) {
@@ -733,6 +745,102 @@ __global__ void bias_gelu_tanh_bf16x8_kernel(__nv_bfloat16* __restrict__ out, lo
   st4(out + (size_t)t * out_stride + i + 4, make_float4(f(z1.x), f(z1.y), f(z1.z), f(z1.w)));
 }
 
+// ---------------------------------------------------------------------------------------------------------------------------------
+// Post-norm residual update (blocks whose sublayers take the un-normed stream and are normed on the way out):
+//   y = add [+ add_bias];   x <- x + y * rsqrt(mean(y^2) + eps) * (offset + w) [* ls];   (out_h != null) out_h <- x in the storage type
+// add: rows fp32 if add_f32, else of the storage type.  One block per token; VEC: four elements per access (width a multiple of 4, 16-byte
+// aligned rows).  The sum of squares is over the sublayer's output only, in fp32.
+// ---------------------------------------------------------------------------------------------------------------------------------
+template <typename ST, bool VEC>
+__global__ void post_norm_update_kernel(ST* __restrict__ out_h, float* __restrict__ x, const void* __restrict__ add, int add_f32,
+                                        const float* __restrict__ add_bias, const float* __restrict__ w, const float* __restrict__ ls, float offset,
+                                        float eps, int W) {
+  __shared__ float red[33];
+  const size_t base = (size_t)blockIdx.x * W;
+  constexpr int V = VEC ? 4 : 1;
+  auto load = [&](int i, float (&y)[V]) {
+    if (VEC) {
+      float4 a = add_f32 ? ld4(static_cast<const float*>(add) + base + i) : ld4(static_cast<const ST*>(add) + base + i);
+      if (add_bias != nullptr) { const float4 b = ld4(add_bias + i); a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w; }
+      y[0] = a.x; y[V > 1 ? 1 : 0] = a.y; y[V > 1 ? 2 : 0] = a.z; y[V > 1 ? 3 : 0] = a.w;
+    } else {
+      y[0] = (add_f32 ? static_cast<const float*>(add)[base + i] : ldf(static_cast<const ST*>(add) + base + i)) + (add_bias != nullptr ? add_bias[i] : 0.f);
+    }
+  };
+  float ss = 0.f;
+  for (int i = threadIdx.x * V; i < W; i += blockDim.x * V) {
+    float y[V];
+    load(i, y);
+#pragma unroll
+    for (int k = 0; k < V; ++k) ss += y[k] * y[k];
+  }
+  ss = block_sum(ss, red);
+  const float r = 1.f / sqrtf(ss / (float)W + eps);
+  for (int i = threadIdx.x * V; i < W; i += blockDim.x * V) {
+    float y[V], v[V];
+    load(i, y);
+#pragma unroll
+    for (int k = 0; k < V; ++k) {
+      float u = y[k] * r * (offset + w[i + k]);
+      if (ls != nullptr) u *= ls[i + k];
+      v[k] = x[base + i + k] + u;
+      x[base + i + k] = v[k];
+    }
+    if (out_h != nullptr) {
+      if (VEC) st4(out_h + base + i, make_float4(v[0], v[V > 1 ? 1 : 0], v[V > 1 ? 2 : 0], v[V > 1 ? 3 : 0]));
+      else stf(out_h + base + i, v[0]);
+    }
+  }
+}
+
+// storage-type copy of fp32 rows (the input of a sublayer that takes the un-normed stream)
+template <typename ST>
+__global__ void cast_rows_kernel(ST* __restrict__ out, const float* __restrict__ x, size_t n) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) stf(out + i, x[i]);
+}
+
+// out[t, i] = act(in[t, i] + bias[i]) * (in[t, ff + i] + bias[ff + i])   (bias may be null); act 0: gelu_tanh, 1: silu
+template <typename ST>
+__global__ void bias_gated_act_kernel(ST* __restrict__ out, long long out_stride, const ST* __restrict__ in, long long in_stride,
+                                      const float* __restrict__ bias, int ff, int act) {
+  const int t = blockIdx.x;
+  const int i = blockIdx.y * blockDim.x + threadIdx.x;
+  if (i >= ff) return;
+  const ST* row = in + (size_t)t * in_stride;
+  const float z = ldf(row + i) + (bias != nullptr ? bias[i] : 0.f), u = ldf(row + ff + i) + (bias != nullptr ? bias[ff + i] : 0.f);
+  const float a = act == 1 ? silu_f(z) : 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+  stf(out + (size_t)t * out_stride + i, a * u);
+}
+
+// bfloat16 rows, eight columns per thread
+__global__ void bias_gated_act_bf16x8_kernel(__nv_bfloat16* __restrict__ out, long long out_stride, const __nv_bfloat16* __restrict__ in,
+                                             long long in_stride, const float* __restrict__ bias, int ff, int act) {
+  const int t = blockIdx.x;
+  const int i = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+  if (i >= ff) return;
+  const __nv_bfloat16* row = in + (size_t)t * in_stride;
+  float z[8], u[8];
+  {
+    const float4 a = ld4(row + i), b = ld4(row + i + 4), c = ld4(row + ff + i), d = ld4(row + ff + i + 4);
+    z[0] = a.x; z[1] = a.y; z[2] = a.z; z[3] = a.w; z[4] = b.x; z[5] = b.y; z[6] = b.z; z[7] = b.w;
+    u[0] = c.x; u[1] = c.y; u[2] = c.z; u[3] = c.w; u[4] = d.x; u[5] = d.y; u[6] = d.z; u[7] = d.w;
+  }
+  if (bias != nullptr) {
+    const float4 a = ld4(bias + i), b = ld4(bias + i + 4), c = ld4(bias + ff + i), d = ld4(bias + ff + i + 4);
+    z[0] += a.x; z[1] += a.y; z[2] += a.z; z[3] += a.w; z[4] += b.x; z[5] += b.y; z[6] += b.z; z[7] += b.w;
+    u[0] += c.x; u[1] += c.y; u[2] += c.z; u[3] += c.w; u[4] += d.x; u[5] += d.y; u[6] += d.z; u[7] += d.w;
+  }
+  float y[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const float arg = act == 1 ? z[k] : 2.f * 0.7978845608028654f * (z[k] + 0.044715f * z[k] * z[k] * z[k]);  // z sigmoid(arg) is silu or gelu_tanh
+    y[k] = __fdividef(z[k], 1.f + fast_exp2(-1.4426950408889634f * arg)) * u[k];
+  }
+  st4(out + (size_t)t * out_stride + i, make_float4(y[0], y[1], y[2], y[3]));
+  st4(out + (size_t)t * out_stride + i + 4, make_float4(y[4], y[5], y[6], y[7]));
+}
+
 // x <- cap * tanh(x / cap), fp32 in place
 __global__ void softcap_kernel(float* __restrict__ x, size_t n, float cap) {
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -822,8 +930,9 @@ int qs_hyb_branch_norm_mean(float* y, const void* a, const void* b, const float*
 int qs_hyb_qk_prepare_append(void* proj, int64_t stride, const float* bias, const float* q_factor, const int32_t* tok_slot, const int32_t* tok_pos,
                              const int32_t* block_table, int max_blocks, void* kpool, void* vpool, const float* inv_freq, int rot_layout,
                              int rot_dims, int unit_rms, float eps, int tokens_n, int heads, int kv_heads, int dim, int vdim, int page_size,
-                             int dtype, void* stream) {
+                             const float* q_gain, const float* k_gain, int tied_values, int dtype, void* stream) {
   QS_REQUIRE(proj && tok_slot && tok_pos && block_table && kpool && vpool, "hyb_qk_prepare_append: null tensor");
+  QS_REQUIRE(!tied_values || vdim == dim, "hyb_qk_prepare_append: values tied to the keys need vdim == dim");
   QS_REQUIRE(rot_dims >= 0 && rot_dims % 2 == 0 && rot_dims <= dim && (rot_dims == 0 || inv_freq != nullptr) && (rot_layout == 0 || rot_layout == 1),
              "hyb_qk_prepare_append: bad rotary size or layout");
   QS_REQUIRE(kv_heads > 0 && heads % kv_heads == 0 && page_size > 0 && dim > 0 && dim <= 8192, "hyb_qk_prepare_append: bad head geometry");
@@ -834,10 +943,11 @@ int qs_hyb_qk_prepare_append(void* proj, int64_t stride, const float* bias, cons
   QS_DT(dtype,
         (qk_prepare_append_kernel<__nv_bfloat16><<<grid, 64, smb, s>>>((__nv_bfloat16*)proj, stride, bias, q_factor, tok_slot, tok_pos, block_table,
                                                                         max_blocks, (__nv_bfloat16*)kpool, (__nv_bfloat16*)vpool, inv_freq, rot_layout,
-                                                                        rot_dims, unit_rms, eps, heads, kv_heads, dim, vdim, page_size)),
+                                                                        rot_dims, unit_rms, eps, heads, kv_heads, dim, vdim, page_size, q_gain, k_gain,
+                                                                        tied_values)),
         (qk_prepare_append_kernel<float><<<grid, 64, smb, s>>>((float*)proj, stride, bias, q_factor, tok_slot, tok_pos, block_table, max_blocks,
                                                                 (float*)kpool, (float*)vpool, inv_freq, rot_layout, rot_dims, unit_rms, eps, heads,
-                                                                kv_heads, dim, vdim, page_size)));
+                                                                kv_heads, dim, vdim, page_size, q_gain, k_gain, tied_values)));
   return check_cuda(cudaGetLastError(), "hyb_qk_prepare_append");
 }
 
@@ -978,6 +1088,53 @@ int qs_hyb_bias_gelu_tanh(void* out, int64_t out_stride, const void* in, int64_t
   QS_DT(dtype, (bias_gelu_tanh_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)in, in_stride, bias, ff)),
         (bias_gelu_tanh_kernel<float><<<grid, 256, 0, s>>>((float*)out, out_stride, (const float*)in, in_stride, bias, ff)));
   return check_cuda(cudaGetLastError(), "hyb_bias_gelu_tanh");
+}
+
+int qs_hyb_post_norm_update(void* out_h, float* x, const void* add, int add_f32, const float* add_bias, const float* w, const float* ls, float offset,
+                            float eps, int tokens_n, int width, int dtype, void* stream) {
+  QS_REQUIRE(x && add && w, "hyb_post_norm_update: null tensor");
+  if (tokens_n == 0) return qs::QS_OK;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int threads = width >= 1024 ? 256 : 128;
+  auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  if (width % 4 == 0 && al16(out_h) && al16(x) && al16(add) && al16(add_bias) && al16(w) && al16(ls)) {
+    QS_DT(dtype,
+          (post_norm_update_kernel<__nv_bfloat16, true><<<tokens_n, threads, 0, s>>>((__nv_bfloat16*)out_h, x, add, add_f32, add_bias, w, ls, offset, eps, width)),
+          (post_norm_update_kernel<float, true><<<tokens_n, threads, 0, s>>>((float*)out_h, x, add, add_f32, add_bias, w, ls, offset, eps, width)));
+  } else {
+    QS_DT(dtype,
+          (post_norm_update_kernel<__nv_bfloat16, false><<<tokens_n, threads, 0, s>>>((__nv_bfloat16*)out_h, x, add, add_f32, add_bias, w, ls, offset, eps, width)),
+          (post_norm_update_kernel<float, false><<<tokens_n, threads, 0, s>>>((float*)out_h, x, add, add_f32, add_bias, w, ls, offset, eps, width)));
+  }
+  return check_cuda(cudaGetLastError(), "hyb_post_norm_update");
+}
+
+int qs_hyb_cast_rows(void* out, const float* x, int64_t n, int dtype, void* stream) {
+  QS_REQUIRE(out && x, "hyb_cast_rows: null tensor");
+  if (n == 0) return qs::QS_OK;
+  cudaStream_t s = (cudaStream_t)stream;
+  const unsigned blocks = (unsigned)((n + 255) / 256);
+  QS_DT(dtype, (cast_rows_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>((__nv_bfloat16*)out, x, (size_t)n)),
+        (cast_rows_kernel<float><<<blocks, 256, 0, s>>>((float*)out, x, (size_t)n)));
+  return check_cuda(cudaGetLastError(), "hyb_cast_rows");
+}
+
+int qs_hyb_bias_gated_act(void* out, int64_t out_stride, const void* in, int64_t in_stride, const float* bias, int tokens_n, int ff, int act, int dtype,
+                          void* stream) {
+  QS_REQUIRE(out && in, "hyb_bias_gated_act: null tensor");
+  QS_REQUIRE(act == QS_ACT_GELU_TANH || act == QS_ACT_SILU, "hyb_bias_gated_act: unknown activation");
+  if (tokens_n == 0) return qs::QS_OK;
+  cudaStream_t s = (cudaStream_t)stream;
+  auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  if (dtype == QS_DTYPE_BF16 && ff % 8 == 0 && out_stride % 8 == 0 && in_stride % 8 == 0 && al16(out) && al16(in) && al16(bias)) {
+    bias_gated_act_bf16x8_kernel<<<dim3(tokens_n, (ff / 8 + 255) / 256), 256, 0, s>>>((__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)in, in_stride,
+                                                                                     bias, ff, act);
+    return check_cuda(cudaGetLastError(), "hyb_bias_gated_act");
+  }
+  dim3 grid(tokens_n, (ff + 255) / 256);
+  QS_DT(dtype, (bias_gated_act_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)in, in_stride, bias, ff, act)),
+        (bias_gated_act_kernel<float><<<grid, 256, 0, s>>>((float*)out, out_stride, (const float*)in, in_stride, bias, ff, act)));
+  return check_cuda(cudaGetLastError(), "hyb_bias_gated_act");
 }
 
 int qs_hyb_softcap(float* x, int64_t n, float cap, void* stream) {

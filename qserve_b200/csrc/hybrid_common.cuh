@@ -108,5 +108,20 @@ __host__ __device__ __forceinline__ int first_key(int pos, int chunk, int window
   return f;
 }
 
+// With a window, the first `keep` positions of a sequence may stay visible.  A walk over tiles of KT keys that starts at tile first / KT then
+// also visits the tiles that hold kept positions before it: n_pre of them, tiles 0 .. n_pre - 1; walk index i stands for tile
+// i < n_pre ? i : first / KT + i - n_pre.
+__host__ __device__ __forceinline__ int kept_tiles(int first, int keep, int KT) { return min((keep + KT - 1) / KT, first / KT); }
+__host__ __device__ __forceinline__ bool key_visible(int kpos, int qpos, int first, int keep) { return kpos <= qpos && (kpos >= first || kpos < keep); }
+
+// optional parts of an attention kernel (qs_attn_extra of the C interface, by value)
+struct AttnExtra {
+  int keep_first;
+  const float* slopes;
+  const void* gate;
+  long long gate_stride;
+};
+__device__ __forceinline__ float sigmoid_f(float z) { return 1.f / (1.f + expf(-z)); }
+
 }  // namespace hyb
 }  // namespace qs

@@ -33,14 +33,16 @@ using namespace hyb;
 // shared rotated key part.
 //   cq[t] = row_q * rsqrt(mean(row_q^2) + eps) * gain_q                         (storage type, feeds the query up-projection)
 //   cell  = [row_c * rsqrt(mean(row_c^2) + eps) * gain_kv | rotate(row_r)]      (storage type, in the token's page)
-// Rotation ("half" layout): entry i < dims/2 is paired with entry i + dims/2, angle = position * inv_freq[i]; entries from `dims` on pass.
+// Rotation: layout 1 ("half") pairs entry i < dims/2 with entry i + dims/2, layout 0 ("interleaved") pairs entries (2i, 2i + 1); angle =
+// position * inv_freq[i], cos and sin times `amp`; entries from `dims` on pass.  Q == 0: there is no query latent (cq is not written).
 // ---------------------------------------------------------------------------------------------------------------------------------
 template <typename ST>
 __global__ void __launch_bounds__(128) latent_prepare_kernel(ST* __restrict__ cq, const ST* __restrict__ proj, long long stride, int col_q, int col_kv,
                                                              const float* __restrict__ gain_q, const float* __restrict__ gain_kv,
                                                              const float* __restrict__ inv_freq, int rot_dims, const int* __restrict__ tok_slot,
                                                              const int* __restrict__ tok_pos, const int* __restrict__ block_table, int max_blocks,
-                                                             ST* __restrict__ pool, int Q, int K, int R, int page, float eps) {
+                                                             ST* __restrict__ pool, int Q, int K, int R, int page, float eps, int rot_layout,
+                                                             float amp) {
   __shared__ float red[33];
   const int t = blockIdx.x, tid = threadIdx.x;
   const ST* row = proj + (size_t)t * stride;
@@ -56,7 +58,7 @@ __global__ void __launch_bounds__(128) latent_prepare_kernel(ST* __restrict__ cq
   }
   sq = block_sum(sq, red);
   sk = block_sum(sk, red);
-  const float rq = 1.f / sqrtf(sq / (float)Q + eps), rk = 1.f / sqrtf(sk / (float)K + eps);
+  const float rq = Q > 0 ? 1.f / sqrtf(sq / (float)Q + eps) : 0.f, rk = 1.f / sqrtf(sk / (float)K + eps);
   for (int i = tid; i < Q; i += blockDim.x) stf(cq + (size_t)t * Q + i, ldf(row + col_q + i) * rq * gain_q[i]);
   const int pg = block_table[(size_t)tok_slot[t] * max_blocks + pos / page];
   ST* cell = pool + ((size_t)pg * page + pos % page) * (size_t)(K + R);
@@ -66,11 +68,12 @@ __global__ void __launch_bounds__(128) latent_prepare_kernel(ST* __restrict__ cq
   for (int i = tid; i < R; i += blockDim.x) {
     float v = ldf(kr + i);
     if (i < rot_dims) {
-      const int p = i < half ? i : i - half;
+      const bool first = rot_layout == 0 ? (i & 1) == 0 : i < half;
+      const int p = rot_layout == 0 ? i >> 1 : (first ? i : i - half);
       float s, c;
       sincosf((float)pos * inv_freq[p], &s, &c);
-      const float a = ldf(kr + p), b = ldf(kr + p + half);
-      v = i < half ? a * c - b * s : b * c + a * s;
+      const float a = ldf(kr + (rot_layout == 0 ? 2 * p : p)), b = ldf(kr + (rot_layout == 0 ? 2 * p + 1 : p + half));
+      v = (first ? a * c - b * s : b * c + a * s) * amp;
     }
     stf(cell + K + i, v);
   }
@@ -82,7 +85,7 @@ __global__ void __launch_bounds__(128) latent_prepare_kernel(ST* __restrict__ cq
 template <typename ST>
 __global__ void __launch_bounds__(64) latent_query_kernel(ST* __restrict__ qa, const ST* __restrict__ qlat, ST* __restrict__ q, long long q_stride,
                                                           const float* __restrict__ inv_freq, int rot_dims, const int* __restrict__ tok_pos, int T, int H,
-                                                          int D, int K, int R, int rotate_back) {
+                                                          int D, int K, int R, int rotate_back, int rot_layout, float amp) {
   const int t = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
   ST* dst = qa != nullptr ? qa + ((size_t)t * H + h) * (size_t)(K + R) : nullptr;
   if (dst != nullptr) {
@@ -94,15 +97,16 @@ __global__ void __launch_bounds__(64) latent_query_kernel(ST* __restrict__ qa, c
   for (int p = tid; p < half; p += blockDim.x) {
     float s, c;
     sincosf((float)pos * inv_freq[p], &s, &c);
-    const float a = ldf(qr + p), b = ldf(qr + p + half);
-    const float u = a * c - b * s, v = b * c + a * s;
+    const int ia = rot_layout == 0 ? 2 * p : p, ib = rot_layout == 0 ? 2 * p + 1 : p + half;
+    const float a = ldf(qr + ia), b = ldf(qr + ib);
+    const float u = (a * c - b * s) * amp, v = (b * c + a * s) * amp;
     if (dst != nullptr) {
-      stf(dst + K + p, u);
-      stf(dst + K + p + half, v);
+      stf(dst + K + ia, u);
+      stf(dst + K + ib, v);
     }
     if (rotate_back) {
-      stf(qr + p, u);
-      stf(qr + p + half, v);
+      stf(qr + ia, u);
+      stf(qr + ib, v);
     }
   }
   if (dst != nullptr)
@@ -129,7 +133,7 @@ template <typename ST, int HPW>
 __global__ void __launch_bounds__(128) latent_attention_kernel(ST* __restrict__ out, const ST* __restrict__ qa, const ST* __restrict__ pool,
                                                                const int* __restrict__ tok_slot, const int* __restrict__ tok_pos,
                                                                const int* __restrict__ block_table, int max_blocks, int T, int H, int K, int R,
-                                                               float scale, int page, int chunk, int window) {
+                                                               float scale, int page, int chunk, int window, const float* __restrict__ sinks) {
   extern __shared__ __align__(16) unsigned char dyn_raw[];
   const int DK = K + R, SD = lat_row_stride<ST>(DK);
   float* qs = reinterpret_cast<float*>(dyn_raw);                 // [4 HPW][DK]
@@ -146,8 +150,11 @@ __global__ void __launch_bounds__(128) latent_attention_kernel(ST* __restrict__ 
   float m_run[HPW], l_run[HPW], acc[HPW][kLatMaxVC];
 #pragma unroll
   for (int u = 0; u < HPW; ++u) {
-    m_run[u] = -INFINITY;
-    l_run[u] = 0.f;
+    // a sink is one more term exp(sink) of the denominator without a value: the running maximum and sum start from it
+    const int hh = h0 + warp * HPW + u;
+    const bool sunk = sinks != nullptr && hh < H;
+    m_run[u] = sunk ? sinks[hh] : -INFINITY;
+    l_run[u] = sunk ? 1.f : 0.f;
 #pragma unroll
     for (int i = 0; i < kLatMaxVC; ++i) acc[u][i] = 0.f;
   }
@@ -220,7 +227,8 @@ __global__ void __launch_bounds__(128) latent_attention_kernel(ST* __restrict__ 
 
 template <typename ST, int HPW>
 int launch_latent_attention(void* out, const void* qa, const void* pool, const int* tok_slot, const int* tok_pos, const int* block_table,
-                            int max_blocks, int T, int H, int K, int R, float scale, int page, int chunk, int window, cudaStream_t s) {
+                            int max_blocks, int T, int H, int K, int R, float scale, int page, int chunk, int window, const float* sinks,
+                            cudaStream_t s) {
   const int DK = K + R;
   const size_t smem = (size_t)4 * HPW * (DK + kLatKT) * sizeof(float) + (size_t)kLatKT * lat_row_stride<ST>(DK) * sizeof(ST);
   QS_REQUIRE(smem <= 200 * 1024, "hyb_latent_attention: latent row too wide for shared memory");
@@ -232,7 +240,7 @@ int launch_latent_attention(void* out, const void* qa, const void* pool, const i
     attr_set[device_ordinal()] = true;
   }
   latent_attention_kernel<ST, HPW><<<dim3(T, (H + 4 * HPW - 1) / (4 * HPW)), 128, smem, s>>>((ST*)out, (const ST*)qa, (const ST*)pool, tok_slot, tok_pos,
-                                                                                          block_table, max_blocks, T, H, K, R, scale, page, chunk, window);
+                                                                                          block_table, max_blocks, T, H, K, R, scale, page, chunk, window, sinks);
   return check_cuda(cudaGetLastError(), "hyb_latent_attention");
 }
 
@@ -267,7 +275,7 @@ __global__ void __launch_bounds__(256, 1) latent_tile_kernel(
     const int* __restrict__ tile_entry, const int* __restrict__ tile_row0, const int* __restrict__ short_tokens, const int* __restrict__ tok_slot,
     const int* __restrict__ tok_pos, const int* __restrict__ entry_start, const int* __restrict__ entry_len, const int* __restrict__ entry_slot,
     const int* __restrict__ entry_pos0, const int* __restrict__ block_table, int max_blocks, int T, int H, int HB, int R, float scale, int page,
-    int chunk, int window, int splits) {
+    int chunk, int window, int splits, const float* __restrict__ sinks) {
   extern __shared__ __align__(16) unsigned char smraw[];
   constexpr int K = 32 * NVT, KG = LtShape<RB>::KG, KT = LtShape<RB>::KT, KW = LtShape<RB>::KW, QR = LtShape<RB>::QR, TPR = 256 / KT;
   const int DK = K + R, DKP = (DK + 15) & ~15, SD = DKP + kLtPad;
@@ -485,7 +493,8 @@ __global__ void __launch_bounds__(256, 1) latent_tile_kernel(
 #pragma unroll
       for (int i = 0; i < 2 * NVT; ++i) *reinterpret_cast<float2*>(dst + 2 + col0 + i * 8) = make_float2(o[i][2 * r], o[i][2 * r + 1]);
     } else {
-      const float inv = 1.f / l_run[r];
+      // a sink joins the denominator as exp(sink) relative to the running maximum (base-2 domain); it has no value
+      const float inv = 1.f / (l_run[r] + (sinks != nullptr ? fast_exp2(sinks[hh] * 1.4426950408889634f - m_run[r]) : 0.f));
       __nv_bfloat16* dst = out + ((size_t)hh * T + tok0 + tk) * (size_t)K + col0;
 #pragma unroll
       for (int i = 0; i < 2 * NVT; ++i) *reinterpret_cast<uint32_t*>(dst + i * 8) = pack_bf16(o[i][2 * r] * inv, o[i][2 * r + 1] * inv);
@@ -495,14 +504,15 @@ __global__ void __launch_bounds__(256, 1) latent_tile_kernel(
 
 // out[h][t][:] = sum_z 2^(m_z - M) o_z / sum_z 2^(m_z - M) l_z over the key shares of a listed token.  One warp per (listed token, head).
 __global__ void latent_merge_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict__ part, const int* __restrict__ short_tokens, int n_short,
-                                    int T, int H, int K, int splits) {
+                                    int T, int H, int K, int splits, const float* __restrict__ sinks) {
   const int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   if (w >= n_short * H) return;
   const int i = w / H, h = w - i * H;
   const float* p = part + (size_t)w * splits * (2 + K);
-  float M = -INFINITY;
+  const float sink2 = sinks != nullptr ? sinks[h] * 1.4426950408889634f : -INFINITY;  // the sink: a share of maximum sink, sum 1, no output
+  float M = sink2;
   for (int z = 0; z < splits; ++z) M = fmaxf(M, p[(size_t)z * (2 + K)]);
-  float L = 0.f;
+  float L = sinks != nullptr ? fast_exp2(sink2 - M) : 0.f;
   for (int z = 0; z < splits; ++z) {
     const float m = p[(size_t)z * (2 + K)];
     if (m != -INFINITY) L += fast_exp2(m - M) * p[(size_t)z * (2 + K) + 1];
@@ -548,7 +558,7 @@ int latent_splits(int n_short, int heads) {
 template <int NVT, int RB>
 int launch_latent_short(void* out, float* part, const void* qa, const void* pool, const int* short_tokens, int n_short, const int* tok_slot,
                         const int* tok_pos, const int* block_table, int max_blocks, int T, int H, int HB, int R, float scale, int page, int chunk,
-                        int window, cudaStream_t s) {
+                        int window, const float* sinks, cudaStream_t s) {
   const int K = 32 * NVT, groups = (H + HB - 1) / HB, splits = latent_splits(n_short, H);
   const size_t smem = latent_tile_smem<RB>(K, R);
   static bool attr_set[kMaxDevices] = {};
@@ -558,9 +568,9 @@ int launch_latent_short(void* out, float* part, const void* qa, const void* pool
   }
   latent_tile_kernel<NVT, RB, true><<<dim3(n_short, groups, splits), 256, smem, s>>>(
       (__nv_bfloat16*)out, part, (const __nv_bfloat16*)qa, (const __nv_bfloat16*)pool, nullptr, nullptr, short_tokens, tok_slot, tok_pos, nullptr, nullptr,
-      nullptr, nullptr, block_table, max_blocks, T, H, HB, R, scale, page, chunk, window, splits);
+      nullptr, nullptr, block_table, max_blocks, T, H, HB, R, scale, page, chunk, window, splits, nullptr);
   const int warps = n_short * H;
-  latent_merge_kernel<<<(warps + 3) / 4, 128, 0, s>>>((__nv_bfloat16*)out, part, short_tokens, n_short, T, H, K, splits);
+  latent_merge_kernel<<<(warps + 3) / 4, 128, 0, s>>>((__nv_bfloat16*)out, part, short_tokens, n_short, T, H, K, splits, sinks);
   return check_cuda(cudaGetLastError(), "hyb_latent_attention_fast single tokens");
 }
 
@@ -568,7 +578,7 @@ template <int NVT>
 int launch_latent_tiles(void* out, float* part, const void* qa, const void* pool, const int* tile_entry, const int* tile_row0, int n_tiles,
                         const int* short_tokens, int n_short, const int* tok_slot, const int* tok_pos, const int* entry_start, const int* entry_len,
                         const int* entry_slot, const int* entry_pos0, const int* block_table, int max_blocks, int T, int H, int R, float scale,
-                        int page, int chunk, int window, cudaStream_t s) {
+                        int page, int chunk, int window, const float* sinks, cudaStream_t s) {
   const int K = 32 * NVT, HB = latent_head_block(H), groups = (H + HB - 1) / HB;
   if (n_tiles > 0) {
     const size_t smem = latent_tile_smem<4>(K, R);
@@ -579,31 +589,31 @@ int launch_latent_tiles(void* out, float* part, const void* qa, const void* pool
     }
     latent_tile_kernel<NVT, 4, false><<<dim3(n_tiles * (kLtTokensPerSpan / (kLtRows / HB)), groups), 256, smem, s>>>(
         (__nv_bfloat16*)out, nullptr, (const __nv_bfloat16*)qa, (const __nv_bfloat16*)pool, tile_entry, tile_row0, nullptr, tok_slot, tok_pos, entry_start,
-        entry_len, entry_slot, entry_pos0, block_table, max_blocks, T, H, HB, R, scale, page, chunk, window, 1);
+        entry_len, entry_slot, entry_pos0, block_table, max_blocks, T, H, HB, R, scale, page, chunk, window, 1, sinks);
     if (int rc = check_cuda(cudaGetLastError(), "hyb_latent_attention_fast tiles")) return rc;
   }
   if (n_short > 0) {
     // a single token has HB live rows: 16 (one row block, four key groups), 32 (two and two) or 64 (four row blocks)
-    if (HB == 16) return launch_latent_short<NVT, 1>(out, part, qa, pool, short_tokens, n_short, tok_slot, tok_pos, block_table, max_blocks, T, H, HB, R, scale, page, chunk, window, s);
-    if (HB == 32) return launch_latent_short<NVT, 2>(out, part, qa, pool, short_tokens, n_short, tok_slot, tok_pos, block_table, max_blocks, T, H, HB, R, scale, page, chunk, window, s);
-    return launch_latent_short<NVT, 4>(out, part, qa, pool, short_tokens, n_short, tok_slot, tok_pos, block_table, max_blocks, T, H, HB, R, scale, page, chunk, window, s);
+    if (HB == 16) return launch_latent_short<NVT, 1>(out, part, qa, pool, short_tokens, n_short, tok_slot, tok_pos, block_table, max_blocks, T, H, HB, R, scale, page, chunk, window, sinks, s);
+    if (HB == 32) return launch_latent_short<NVT, 2>(out, part, qa, pool, short_tokens, n_short, tok_slot, tok_pos, block_table, max_blocks, T, H, HB, R, scale, page, chunk, window, sinks, s);
+    return launch_latent_short<NVT, 4>(out, part, qa, pool, short_tokens, n_short, tok_slot, tok_pos, block_table, max_blocks, T, H, HB, R, scale, page, chunk, window, sinks, s);
   }
   return qs::QS_OK;
 }
 
-// out[t][h * Dv + j] = o * sigmoid(gate[t][col_g + h])   (gate == null: no gate).  o = ov[h][t][j] (head-major rows of the value
+// out[t][h * Dv + j] = o * sigmoid(gate[t][col_g + h])   (gate == null: no gate; gate_wide: gate[t][col_g + h * Dv + j]).  o = ov[h][t][j] (head-major rows of the value
 // up-projection), or, for tokens of entries of at least min_long tokens when `alt` is given, alt[t][h * Dv + j] (token-major rows of the
 // per-head attention over a prompt portion).  One block per token.
 template <typename ST>
 __global__ void latent_gate_out_kernel(ST* __restrict__ out, long long out_stride, const ST* __restrict__ ov, const ST* __restrict__ alt,
                                        long long alt_stride, const int* __restrict__ tok_entry, const int* __restrict__ entry_len, int min_long,
-                                       const ST* __restrict__ gate, long long gate_stride, int col_g, int T, int H, int Dv) {
+                                       const ST* __restrict__ gate, long long gate_stride, int col_g, int T, int H, int Dv, int gate_wide) {
   const int t = blockIdx.x;
   const bool from_alt = alt != nullptr && entry_len[tok_entry[t]] >= min_long;
   for (int i = threadIdx.x; i < H * Dv; i += blockDim.x) {
     const int h = i / Dv, j = i - h * Dv;
     float v = from_alt ? ldf(alt + (size_t)t * alt_stride + i) : ldf(ov + ((size_t)h * T + t) * Dv + j);
-    if (gate != nullptr) v *= 1.f / (1.f + expf(-ldf(gate + (size_t)t * gate_stride + col_g + h)));
+    if (gate != nullptr) v *= 1.f / (1.f + expf(-ldf(gate + (size_t)t * gate_stride + col_g + (gate_wide ? i : h))));
     stf(out + (size_t)t * out_stride + i, v);
   }
 }
@@ -624,25 +634,28 @@ extern "C" {
 
 int qs_hyb_latent_prepare(void* cq, const void* proj, int64_t stride, int col_q, int col_kv, const float* gain_q, const float* gain_kv,
                           const float* inv_freq, int rot_dims, const int32_t* tok_slot, const int32_t* tok_pos, const int32_t* block_table,
-                          int max_blocks, void* pool, int tokens_n, int q_rank, int kv_rank, int rot_dim, int page_size, float eps, int dtype,
-                          void* stream) {
-  QS_REQUIRE(cq && proj && gain_q && gain_kv && tok_slot && tok_pos && block_table && pool, "hyb_latent_prepare: null tensor");
-  QS_REQUIRE(q_rank > 0 && kv_rank > 0 && rot_dim >= 0 && page_size > 0, "hyb_latent_prepare: bad sizes");
+                          int max_blocks, void* pool, int tokens_n, int q_rank, int kv_rank, int rot_dim, int page_size, float eps, int rot_layout,
+                          float amplitude, int dtype, void* stream) {
+  QS_REQUIRE(proj && gain_kv && tok_slot && tok_pos && block_table && pool && (q_rank == 0 || (cq && gain_q)), "hyb_latent_prepare: null tensor");
+  QS_REQUIRE(q_rank >= 0 && kv_rank > 0 && rot_dim >= 0 && page_size > 0 && (rot_layout == 0 || rot_layout == 1), "hyb_latent_prepare: bad sizes");
   QS_REQUIRE(rot_dims % 2 == 0 && rot_dims >= 0 && rot_dims <= rot_dim && (rot_dims == 0 || inv_freq), "hyb_latent_prepare: bad rotation");
   if (tokens_n == 0) return qs::QS_OK;
   cudaStream_t s = (cudaStream_t)stream;
   QS_DT(dtype,
         (latent_prepare_kernel<__nv_bfloat16><<<tokens_n, 128, 0, s>>>((__nv_bfloat16*)cq, (const __nv_bfloat16*)proj, stride, col_q, col_kv, gain_q,
                                                                         gain_kv, inv_freq, rot_dims, tok_slot, tok_pos, block_table, max_blocks,
-                                                                        (__nv_bfloat16*)pool, q_rank, kv_rank, rot_dim, page_size, eps)),
+                                                                        (__nv_bfloat16*)pool, q_rank, kv_rank, rot_dim, page_size, eps, rot_layout,
+                                                                        amplitude)),
         (latent_prepare_kernel<float><<<tokens_n, 128, 0, s>>>((float*)cq, (const float*)proj, stride, col_q, col_kv, gain_q, gain_kv, inv_freq,
                                                                rot_dims, tok_slot, tok_pos, block_table, max_blocks, (float*)pool, q_rank, kv_rank,
-                                                               rot_dim, page_size, eps)));
+                                                               rot_dim, page_size, eps, rot_layout, amplitude)));
   return check_cuda(cudaGetLastError(), "hyb_latent_prepare");
 }
 
 int qs_hyb_latent_query(void* qa, const void* qlat, void* q, int64_t q_stride, const float* inv_freq, int rot_dims, const int32_t* tok_pos,
-                        int tokens_n, int heads, int dim, int kv_rank, int rot_dim, int rotate_back, int dtype, void* stream) {
+                        int tokens_n, int heads, int dim, int kv_rank, int rot_dim, int rotate_back, int rot_layout, float amplitude, int dtype,
+                        void* stream) {
+  QS_REQUIRE(rot_layout == 0 || rot_layout == 1, "hyb_latent_query: unknown rotary layout");
   QS_REQUIRE(q && tok_pos && (qa == nullptr || qlat != nullptr) && (qa != nullptr || rotate_back), "hyb_latent_query: null tensor");
   QS_REQUIRE(rot_dims % 2 == 0 && rot_dims >= 0 && rot_dims <= rot_dim && (rot_dims == 0 || inv_freq), "hyb_latent_query: bad rotation");
   if (tokens_n == 0) return qs::QS_OK;
@@ -650,15 +663,15 @@ int qs_hyb_latent_query(void* qa, const void* qlat, void* q, int64_t q_stride, c
   dim3 grid(tokens_n, heads);
   QS_DT(dtype,
         (latent_query_kernel<__nv_bfloat16><<<grid, 64, 0, s>>>((__nv_bfloat16*)qa, (const __nv_bfloat16*)qlat, (__nv_bfloat16*)q, q_stride, inv_freq, rot_dims,
-                                                                 tok_pos, tokens_n, heads, dim, kv_rank, rot_dim, rotate_back)),
+                                                                 tok_pos, tokens_n, heads, dim, kv_rank, rot_dim, rotate_back, rot_layout, amplitude)),
         (latent_query_kernel<float><<<grid, 64, 0, s>>>((float*)qa, (const float*)qlat, (float*)q, q_stride, inv_freq, rot_dims, tok_pos, tokens_n, heads, dim,
-                                                         kv_rank, rot_dim, rotate_back)));
+                                                         kv_rank, rot_dim, rotate_back, rot_layout, amplitude)));
   return check_cuda(cudaGetLastError(), "hyb_latent_query");
 }
 
 int qs_hyb_latent_attention(void* out, const void* qa, const void* pool, const int32_t* tok_slot, const int32_t* tok_pos, const int32_t* block_table,
                             int max_blocks, int tokens_n, int heads, int kv_rank, int rot_dim, float scale, int page_size, int chunk, int window,
-                            int dtype, void* stream) {
+                            const float* sinks, int dtype, void* stream) {
   QS_REQUIRE(out && qa && pool && tok_slot && tok_pos && block_table, "hyb_latent_attention: null tensor");
   QS_REQUIRE(heads > 0 && kv_rank > 0 && kv_rank <= 32 * kLatMaxVC && rot_dim >= 0 && page_size > 0, "hyb_latent_attention: bad sizes (kv_rank <= 512)");
   QS_REQUIRE(chunk >= 0 && window >= 0, "hyb_latent_attention: negative chunk or window");
@@ -667,11 +680,11 @@ int qs_hyb_latent_attention(void* out, const void* qa, const void* pool, const i
 #define QS_LAT(ST)                                                                                                                               \
   do {                                                                                                                                           \
     if (heads > 8) return launch_latent_attention<ST, 4>(out, qa, pool, tok_slot, tok_pos, block_table, max_blocks, tokens_n, heads, kv_rank, rot_dim, \
-                                                         scale, page_size, chunk, window, s);                                                   \
+                                                         scale, page_size, chunk, window, sinks, s);                                            \
     if (heads > 4) return launch_latent_attention<ST, 2>(out, qa, pool, tok_slot, tok_pos, block_table, max_blocks, tokens_n, heads, kv_rank, rot_dim, \
-                                                         scale, page_size, chunk, window, s);                                                   \
+                                                         scale, page_size, chunk, window, sinks, s);                                            \
     return launch_latent_attention<ST, 1>(out, qa, pool, tok_slot, tok_pos, block_table, max_blocks, tokens_n, heads, kv_rank, rot_dim, scale,   \
-                                          page_size, chunk, window, s);                                                                         \
+                                          page_size, chunk, window, sinks, s);                                                                  \
   } while (0)
   QS_DT(dtype, QS_LAT(__nv_bfloat16), QS_LAT(float));
 #undef QS_LAT
@@ -691,7 +704,7 @@ int qs_hyb_latent_attention_fast(void* out, const void* qa, const void* pool, co
                                  int max_blocks, const int32_t* tile_entry, const int32_t* tile_row0, int n_tiles, const int32_t* short_tokens,
                                  int n_short, const int32_t* entry_start, const int32_t* entry_len, const int32_t* entry_slot,
                                  const int32_t* entry_pos0, int tokens_n, float* scratch, int heads, int kv_rank, int rot_dim, float scale,
-                                 int page_size, int chunk, int window, int dtype, void* stream) {
+                                 int page_size, int chunk, int window, const float* sinks, int dtype, void* stream) {
   QS_REQUIRE(out && qa && pool && tok_slot && tok_pos && block_table, "hyb_latent_attention_fast: null tensor");
   QS_REQUIRE(latent_fast_supported(dtype, heads, kv_rank, rot_dim), "hyb_latent_attention_fast: shape not supported (use qs_hyb_latent_attention)");
   QS_REQUIRE(chunk >= 0 && window >= 0 && page_size > 0, "hyb_latent_attention_fast: bad mask or page size");
@@ -700,7 +713,7 @@ int qs_hyb_latent_attention_fast(void* out, const void* qa, const void* pool, co
   cudaStream_t s = (cudaStream_t)stream;
 #define QS_LT(NVT)                                                                                                                              \
   return launch_latent_tiles<NVT>(out, scratch, qa, pool, tile_entry, tile_row0, n_tiles, short_tokens, n_short, tok_slot, tok_pos, entry_start, \
-                                  entry_len, entry_slot, entry_pos0, block_table, max_blocks, tokens_n, heads, rot_dim, scale, page_size, chunk, window, s)
+                                  entry_len, entry_slot, entry_pos0, block_table, max_blocks, tokens_n, heads, rot_dim, scale, page_size, chunk, window, sinks, s)
   switch (kv_rank / 32) {
     case 1: QS_LT(1);
     case 2: QS_LT(2);
@@ -713,7 +726,7 @@ int qs_hyb_latent_attention_fast(void* out, const void* qa, const void* pool, co
 
 int qs_hyb_latent_gate_out(void* out, int64_t out_stride, const void* ov, const void* alt, int64_t alt_stride, const int32_t* tok_entry,
                            const int32_t* entry_len, int min_long, const void* gate, int64_t gate_stride, int col_g, int tokens_n, int heads, int vdim,
-                           int dtype, void* stream) {
+                           int gate_wide, int dtype, void* stream) {
   QS_REQUIRE(out && (ov || alt), "hyb_latent_gate_out: null tensor");
   QS_REQUIRE(alt == nullptr || (tok_entry && entry_len), "hyb_latent_gate_out: the second source needs the entry tables");
   QS_REQUIRE(ov != nullptr || min_long <= 1, "hyb_latent_gate_out: without head-major rows every token must come from the second source");
@@ -722,9 +735,9 @@ int qs_hyb_latent_gate_out(void* out, int64_t out_stride, const void* ov, const 
   QS_DT(dtype,
         (latent_gate_out_kernel<__nv_bfloat16><<<tokens_n, 128, 0, s>>>((__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)ov, (const __nv_bfloat16*)alt,
                                                                          alt_stride, tok_entry, entry_len, min_long, (const __nv_bfloat16*)gate, gate_stride,
-                                                                         col_g, tokens_n, heads, vdim)),
+                                                                         col_g, tokens_n, heads, vdim, gate_wide)),
         (latent_gate_out_kernel<float><<<tokens_n, 128, 0, s>>>((float*)out, out_stride, (const float*)ov, (const float*)alt, alt_stride, tok_entry, entry_len,
-                                                                min_long, (const float*)gate, gate_stride, col_g, tokens_n, heads, vdim)));
+                                                                min_long, (const float*)gate, gate_stride, col_g, tokens_n, heads, vdim, gate_wide)));
   return check_cuda(cudaGetLastError(), "hyb_latent_gate_out");
 }
 

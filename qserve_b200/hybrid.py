@@ -19,14 +19,18 @@ from typing import Dict, List, Optional, Sequence
 
 import torch
 
-from ._lib import check, lib
+import ctypes
+
+from ._lib import AttnExtra, check, lib
 from .cache import HybridCache
-from .modelcfg import (AttentionMixerConfig, DeltaMixerConfig, GateRecurrenceMixerConfig, HybridConfig, LatentAttentionMixerConfig, MlpConfig,
-                       MoeConfig, ParallelMixerConfig, RetentionMixerConfig)
+from .modelcfg import (AttentionMixerConfig, DeltaMixerConfig, GatedLinearMixerConfig, GateRecurrenceMixerConfig, HybridConfig,
+                       LatentAttentionMixerConfig, MlpConfig, MoeConfig, ParallelMixerConfig, RetentionMixerConfig)
 
 _DT = {torch.bfloat16: 0, torch.float32: 1}
 _NORM_KIND = {"rms": 1, "layer": 2}      # QS_NORM_RMS, QS_NORM_LAYER
 _ROUTER_MODE = {"softmax": 0, "sigmoid": 1}  # QS_ROUTER_SOFTMAX, QS_ROUTER_SIGMOID_GROUPS
+_ACT = {"gelu_tanh": 0, "silu": 1}           # QS_ACT_GELU_TANH, QS_ACT_SILU
+_ROT_LAYOUT = {"interleaved": 0, "half": 1}
 _F32_OUT = [None]  # whether torch.mm takes out_dtype on this build (found at first use)
 
 
@@ -40,7 +44,19 @@ def _mm_f32(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
             _F32_OUT[0] = True
         except (TypeError, RuntimeError):
             _F32_OUT[0] = False
-    return torch.mm(a, b, out_dtype=torch.float32) if _F32_OUT[0] else torch.mm(a, b).float()
+    if _F32_OUT[0]:
+        try:
+            return torch.mm(a, b, out_dtype=torch.float32)
+        except RuntimeError:  # a shape or stride this form of the product does not take
+            pass
+    return torch.mm(a, b).float()
+
+
+def _pad_rows(w: torch.Tensor, multiple: int = 8) -> torch.Tensor:
+    """`w` with zero rows added up to a multiple: projection rows whose stride keeps 16-byte alignment in bfloat16 (the tensor-core attention
+    kernels load queries 16 bytes at a time straight from the rows of the mixer's one input product)."""
+    pad = (-w.shape[0]) % multiple
+    return w if pad == 0 else torch.cat([w, torch.zeros((pad, w.shape[1]), dtype=w.dtype, device=w.device)], 0)
 
 
 def _stream(dev: torch.device):
@@ -165,34 +181,54 @@ class _Mixer:
 class MultiMapAttentionMixer(_Mixer):
     """Causal softmax attention over the paged cache with `maps` score maps per head sharing the values; maps = 2 is differential attention:
     o = a1 - lambda a2 with lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + diff, then unit RMS per head and a factor (1 - diff).
-    With one map: optional projection biases, unit-RMS q / k, a learned temperature per head (folded into the prepared query), a sink term in
-    the denominator, and a mask by chunks of positions and / or a window."""
+    With one map: optional projection biases, unit-RMS q / k (with gains shared by the heads), a learned temperature per head (folded into the
+    prepared query), a sink term in the denominator, a mask by chunks of positions and / or a window that may keep the sequence's first
+    positions visible, a linear distance bias per head, values tied to the key projection's raw output (no value projection), and a sigmoid gate per head
+    (its logits are the last `heads` columns of the mixer's projection rows)."""
 
     def __init__(self, m: AttentionMixerConfig, w: Dict[str, torch.Tensor], eps: float, dtype, device):
         self.m, self.eps = m, eps
         assert m.heads % m.kv_heads == 0
         f32 = lambda t: t.to(torch.float32).to(device).contiguous()
-        self.general = m.rot is None or m.rot.layout != "interleaved" or m.bias or m.qk_norm or m.head_temp
-        if (self.general or m.sink) and m.maps != 1:
-            raise ValueError("biases, unit-RMS q / k, head temperatures, sinks and non-interleaved rotations need one score map per head")
-        self.bias = f32(torch.cat([w["q.b"], w["k.b"], w["v.b"]], 0)) if m.bias else None
+        self.general = m.rot is None or m.rot.layout != "interleaved" or m.bias or m.qk_norm or m.head_temp or m.tied_values
+        plus = m.sink or m.keep_first or m.distance_slope > 0.0 or m.head_gate or m.qk_gain
+        if (self.general or plus) and m.maps != 1:
+            raise ValueError("biases, unit-RMS q / k, head temperatures, sinks, kept first positions, distance biases, tied values, head gates and "
+                             "non-interleaved rotations need one score map per head")
+        if m.keep_first and (m.window <= 0 or m.chunk):
+            raise ValueError("kept first positions go with a window and no chunks")
+        if m.tied_values and m.vdim != m.dim:
+            raise ValueError("values tied to the keys need vdim == dim")
+        if m.qk_gain and not m.qk_norm:
+            raise ValueError("q / k gains belong to the unit-RMS q / k")
+        parts = ["q", "k"] + ([] if m.tied_values else ["v"])
+        self.bias = f32(torch.cat([w[n + ".b"] for n in parts], 0)) if m.bias else None
+        self.q_gain, self.k_gain = (f32(w["q.norm"]), f32(w["k.norm"])) if m.qk_gain else (None, None)
+        if m.qk_gain and (self.q_gain.numel() != m.dim or self.k_gain.numel() != m.dim):
+            raise ValueError("q / k gains have `dim` numbers")
+        sl = m.slopes()
+        self.slopes = torch.tensor(sl, dtype=torch.float64).to(torch.float32).to(device) if sl is not None else None
         self.temp = f32(w["temp"]) if m.head_temp else None
         self.sinks = f32(w["sink"]) if m.sink else None
         for t, n in ((self.temp, "temp"), (self.sinks, "sink")):
             if t is not None and t.numel() != m.heads:
                 raise ValueError(f"attention weight {n} must have one number per head")
-        self.in_features = (m.heads + m.kv_heads) * m.maps * m.dim + m.kv_heads * m.vdim
+        self.col_g = (m.heads + m.kv_heads) * m.maps * m.dim + (0 if m.tied_values else m.kv_heads * m.vdim)
+        self.in_features = self.col_g + (m.heads if m.head_gate else 0)
         self.out_features = m.heads * m.vdim
-        for name, rows in (("q", m.heads * m.maps * m.dim), ("k", m.kv_heads * m.maps * m.dim), ("v", m.kv_heads * m.vdim)):
-            if w[name].shape[0] != rows:
-                raise ValueError(f"attention weight {name}: {tuple(w[name].shape)} does not have {rows} rows")
-        self.w_in = torch.cat([w["q"], w["k"], w["v"]], 0).to(device=device, dtype=dtype).contiguous()
+        rows_of = {"q": m.heads * m.maps * m.dim, "k": m.kv_heads * m.maps * m.dim, "v": m.kv_heads * m.vdim, "g": m.heads}
+        parts += ["g"] if m.head_gate else []
+        for name in parts:
+            if w[name].shape[0] != rows_of[name]:
+                raise ValueError(f"attention weight {name}: {tuple(w[name].shape)} does not have {rows_of[name]} rows")
+        self.w_in = _pad_rows(torch.cat([w[n] for n in parts], 0)).to(device=device, dtype=dtype).contiguous()
+        self.in_features = self.w_in.shape[0]
         self.w_out = w["o"]
         self.inv_freq = torch.tensor(m.rot.inv_freq(), dtype=torch.float64).to(torch.float32).to(device) if m.rot is not None else None
         self.amp = float(m.rot.amplitude()) if m.rot is not None else 1.0
         if self.general and self.amp != 1.0:
             raise ValueError("scaled rotary frequencies are only built for the interleaved layout")
-        if self.bias is not None and self.bias.numel() != self.in_features:
+        if self.bias is not None and self.bias.numel() != self.col_g:
             raise ValueError("attention biases do not match the projections")
         if m.maps == 2:
             d = lambda a, b: float((w[a].double() * w[b].double()).sum())
@@ -207,14 +243,19 @@ class MultiMapAttentionMixer(_Mixer):
 
     def run(self, proj: torch.Tensor, out: torch.Tensor, b: StepBatch, run_cache: dict, page_size: int, scratch, dt: int, stream) -> None:
         m = self.m
-        fast = scratch is not None and \
+        fast = scratch is not None and ATTENTION_IMPL != "plain" and \
             lib.qs_hyb_attention_fast_supported(dt, m.heads, m.kv_heads, m.maps, m.dim, m.vdim, proj.stride(0)) == 1
+        extra = None
+        if m.keep_first or self.slopes is not None or m.head_gate:
+            gate = proj.data_ptr() + self.col_g * proj.element_size() if m.head_gate else None
+            extra = ctypes.byref(AttnExtra(m.keep_first, _p(self.slopes), gate, proj.stride(0)))
         if self.general:
             check(lib.qs_hyb_qk_prepare_append(proj.data_ptr(), proj.stride(0), _p(self.bias), _p(self.temp), _p(b.tok_slot), _p(b.tok_pos),
                                                _p(b.block_table), b.block_table.shape[1], run_cache["k"].data_ptr(), run_cache["v"].data_ptr(),
                                                _p(self.inv_freq), 1 if m.rot is not None and m.rot.layout == "half" else 0,
                                                m.rot.dims if m.rot is not None else 0, 1 if m.qk_norm else 0, self.eps, b.n_tokens, m.heads,
-                                               m.kv_heads, m.dim, m.vdim, page_size, dt, stream))
+                                               m.kv_heads, m.dim, m.vdim, page_size, _p(self.q_gain), _p(self.k_gain), 1 if m.tied_values else 0,
+                                               dt, stream))
         else:
             check(lib.qs_hyb_rope_append(proj.data_ptr(), proj.stride(0), _p(b.tok_slot), _p(b.tok_pos), _p(b.block_table), b.block_table.shape[1],
                                          run_cache["k"].data_ptr(), run_cache["v"].data_ptr(), self.inv_freq.data_ptr(), self.amp, b.n_tokens,
@@ -226,12 +267,15 @@ class MultiMapAttentionMixer(_Mixer):
                                             _p(b.tile_entry), _p(b.tile_row0), b.n_tiles, _p(b.long_tokens), b.n_long, _p(b.short_tokens), b.n_short,
                                             _p(b.entry_start), _p(b.entry_len), _p(b.entry_slot), _p(b.entry_pos0), scratch.data_ptr(), m.heads,
                                             m.kv_heads, m.maps, m.dim, m.vdim, m.scale, self.lam, self.out_scale, self.eps,
-                                            1 if m.head_norm else 0, page_size, m.chunk, m.window, _p(self.sinks), dt, stream))
+                                            1 if m.head_norm else 0, page_size, m.chunk, m.window, _p(self.sinks), extra, dt, stream))
             return
         check(lib.qs_hyb_attention(out.data_ptr(), out.stride(0), proj.data_ptr(), proj.stride(0), run_cache["k"].data_ptr(),
                                    run_cache["v"].data_ptr(), _p(b.tok_slot), _p(b.tok_pos), _p(b.block_table), b.block_table.shape[1],
                                    b.n_tokens, m.heads, m.kv_heads, m.maps, m.dim, m.vdim, m.scale, self.lam, self.out_scale, self.eps,
-                                   1 if m.head_norm else 0, page_size, m.chunk, m.window, _p(self.sinks), dt, stream))
+                                   1 if m.head_norm else 0, page_size, m.chunk, m.window, _p(self.sinks), extra, dt, stream))
+
+
+ATTENTION_IMPL = None  # tests: "plain" keeps the attention on the CUDA-core kernel
 
 
 class GatedDeltaMixer(_Mixer):
@@ -333,30 +377,74 @@ class RetentionMixer(_Mixer):
                                    _p(b.entry_slot), _p(b.entry_pos0), T, b.n_entries, m.heads, m.dim, m.vdim, self.eps, dt, stream))
 
 
+class GatedLinearMixer(_Mixer):
+    """Gated linear attention: S <- diag(a) S + k v^T, o = S^T q with q times dim^-1/2 and a decay per head and key channel
+    a = sigmoid(W_a2 (W_a1 h) + b)^(1/tau) (the low-rank projection's first factor is part of the mixer's one input product, its second an fp32
+    product of its own; decay, state and read-out are fp32); unit-RMS heads with a gain shared by the heads, times silu of an output gate.
+    The fp32 state lives in the sequence's slot."""
+
+    def __init__(self, m: GatedLinearMixerConfig, w: Dict[str, torch.Tensor], eps: float, dtype, device):
+        self.m, self.eps = m, eps
+        hd, hv = m.heads * m.dim, m.heads * m.vdim
+        rank = w["a1"].shape[0]
+        if m.decay_rank and rank != m.decay_rank:
+            raise ValueError(f"gated linear attention: a1 has {rank} rows, the configuration says {m.decay_rank}")
+        for name, rows in (("q", hd), ("k", hd), ("v", hv), ("g", hv), ("a2", hd)):
+            if w[name].shape[0] != rows:
+                raise ValueError(f"gated linear attention weight {name}: {tuple(w[name].shape)} does not have {rows} rows")
+        if w["a2"].shape[1] != rank or w["a2.b"].numel() != hd or w["norm"].numel() != m.vdim:
+            raise ValueError("gated linear attention: a2 is [heads * dim, rank], a2.b has heads * dim entries, norm has vdim")
+        self.col_a = 2 * hd + 2 * hv
+        self.in_features, self.out_features = self.col_a + rank, hv
+        self.prep_width = 3 * hd + hv
+        self.w_in = torch.cat([w["q"], w["k"], w["v"], w["g"], w["a1"]], 0).to(device=device, dtype=dtype).contiguous()
+        self.w_a2 = w["a2"].to(device=device, dtype=dtype).contiguous()
+        self.w_out = w["o"]
+        f32 = lambda t: t.to(torch.float32).to(device).contiguous()
+        self.a_bias, self.norm_w = f32(w["a2.b"]), f32(w["norm"])
+
+    def scratch_floats(self, tokens: int) -> int:
+        return tokens * (self.prep_width + self.out_features)
+
+    def run(self, proj, out, b: StepBatch, run_cache: dict, page_size: int, scratch: torch.Tensor, dt: int, stream) -> None:
+        m, T = self.m, b.n_tokens
+        prep = scratch[: T * self.prep_width]
+        o_raw = scratch[T * self.prep_width: T * (self.prep_width + self.out_features)]
+        z = _mm_f32(proj[:, self.col_a:], self.w_a2.t())  # decay logits [T, heads * dim], fp32 from here on
+        check(lib.qs_hyb_gated_linear(out.data_ptr(), out.stride(0), prep.data_ptr(), o_raw.data_ptr(), proj.data_ptr(), proj.stride(0), z.data_ptr(),
+                                      self.a_bias.data_ptr(), m.tau, self.norm_w.data_ptr(), run_cache["state"].data_ptr(), _p(b.entry_start),
+                                      _p(b.entry_len), _p(b.entry_slot), _p(b.entry_pos0), T, b.n_entries, m.heads, m.dim, m.vdim, self.eps, dt, stream))
+
+
 class LatentAttentionMixer(_Mixer):
     """Latent attention: c_q = unit_rms(W_dq h) g_q, q = W_uq c_q (per head `dim` unrotated and `rot_dim` rotated numbers); [c | k_rot] =
     [unit_rms((W_dkv h)[:kv_rank]) g_kv | rotate((W_dkv h)[kv_rank:])] is all the cache holds per position.  Scores
     (q_nope . W_uk c + q_rot . k_rot) * scale are formed as (W_uk^T q_nope) . c + q_rot . k_rot: the key up-projection is applied to the
     query (a batched product over the heads), every head scores the cached rows as they lie in memory, the weighted sum of the latents goes
-    through the value up-projection W_uv (another batched product), and a sigmoid gate of the mixer's input scales each head."""
+    through the value up-projection W_uv (another batched product), and a sigmoid gate of the mixer's input scales each head (or, gate_wide,
+    each output number).  With q_rank 0 there is no query latent: q = W_q h is part of the one input product.  A sink adds exp(sink[h]) to head
+    h's softmax denominators."""
 
     def __init__(self, m: LatentAttentionMixerConfig, w: Dict[str, torch.Tensor], eps: float, dtype, device):
         self.m, self.eps = m, eps
         H, D, R, Dv, K, Q = m.heads, m.dim, m.rot_dim, m.vdim, m.kv_rank, m.q_rank
-        names = (("dq", Q), ("uq", H * (D + R)), ("dkv", K + R), ("uk", H * D), ("uv", H * Dv)) + ((("g", H),) if m.gate else ())
+        HQ, NG = H * (D + R), (H * Dv if m.gate_wide else H)
+        names = ((("dq", Q), ("uq", HQ)) if Q else (("q", HQ),)) + (("dkv", K + R), ("uk", H * D), ("uv", H * Dv)) + ((("g", NG),) if m.gate else ())
         for name, rows in names:
             if w[name].shape[0] != rows:
                 raise ValueError(f"latent attention weight {name}: {tuple(w[name].shape)} does not have {rows} rows")
-        if w["uq"].shape[1] != Q or w["uk"].shape[1] != K or w["uv"].shape[1] != K or w["dq.norm"].numel() != Q or w["dkv.norm"].numel() != K:
+        if w["uk"].shape[1] != K or w["uv"].shape[1] != K or w["dkv.norm"].numel() != K or (Q and (w["uq"].shape[1] != Q or w["dq.norm"].numel() != Q)):
             raise ValueError("latent attention: up-projections and gains do not match q_rank / kv_rank")
         st = lambda t: t.to(device=device, dtype=dtype).contiguous()
         f32 = lambda t: t.to(torch.float32).to(device).contiguous()
-        # one product makes [query latent | key/value latent, rotated key part | gate logits]
-        self.col_q, self.col_kv, self.col_g = 0, Q, Q + K + R
-        self.in_features = Q + K + R + (H if m.gate else 0)
+        # one product makes [query latent (or, without one, the queries) | key/value latent, rotated key part | gate logits]
+        NQ = Q if Q else HQ
+        self.col_q, self.col_kv, self.col_g = 0, NQ, NQ + K + R
+        self.in_features = NQ + K + R + (NG if m.gate else 0)
         self.out_features = H * Dv
-        self.w_in = st(torch.cat([w["dq"], w["dkv"]] + ([w["g"]] if m.gate else []), 0))
-        self.w_uq = st(w["uq"])
+        self.w_in = st(_pad_rows(torch.cat([w["dq"] if Q else w["q"], w["dkv"]] + ([w["g"]] if m.gate else []), 0)))
+        self.in_features = self.w_in.shape[0]
+        self.w_uq = st(w["uq"]) if Q else None
         self.w_uk = st(w["uk"]).view(H, D, K)                                   # q_lat[h] = q_nope[h] @ w_uk[h]
         self.w_uv = st(w["uv"].reshape(H, Dv, K).transpose(1, 2))               # [H, K, Dv]: values[h] = o_lat[h] @ w_uv[h]
         self.w_out = w["o"]
@@ -367,12 +455,15 @@ class LatentAttentionMixer(_Mixer):
         aug[:, D:, K:] = torch.eye(R)
         self.w_keys = st(aug.reshape(H * (D + R), K + R))
         self.w_values = st(w["uv"])
-        self.per_head_ok = lib.qs_hyb_attention_fast_supported(_DT[dtype], H, H, 1, D + R, Dv, H * (D + R)) == 1
-        self.gain_q, self.gain_kv = f32(w["dq.norm"]), f32(w["dkv.norm"])
-        if m.rot is not None and (m.rot.layout != "half" or m.rot.factor is not None):
-            raise ValueError("latent attention rotates pairs (i, i + dims/2) with unscaled frequencies")
+        self.per_head_ok = lib.qs_hyb_attention_fast_supported(_DT[dtype], H, H, 1, D + R, Dv, HQ if Q else self.in_features) == 1
+        self.gain_q, self.gain_kv = f32(w["dq.norm"]) if Q else None, f32(w["dkv.norm"])
         self.inv_freq = torch.tensor(m.rot.inv_freq(), dtype=torch.float64).to(torch.float32).to(device) if m.rot is not None else None
         self.rot_dims = m.rot.dims if m.rot is not None else 0
+        self.rot_layout = _ROT_LAYOUT[m.rot.layout] if m.rot is not None else 0
+        self.amp = float(m.rot.amplitude()) if m.rot is not None else 1.0
+        self.sinks = f32(w["sink"]) if m.sink else None
+        if self.sinks is not None and self.sinks.numel() != H:
+            raise ValueError("latent attention: the sink has one number per head")
 
     def scratch_floats(self, tokens: int) -> int:
         per_head = int(lib.qs_hyb_attention_scratch_floats(tokens, self.m.heads, self.m.heads, 1, self.m.vdim)) if self.per_head_ok else 0
@@ -382,22 +473,22 @@ class LatentAttentionMixer(_Mixer):
         m, T, dev = self.m, b.n_tokens, proj.device
         H, D, R, Dv, K, Q = m.heads, m.dim, m.rot_dim, m.vdim, m.kv_rank, m.q_rank
         pool = run_cache["c"]
-        cq = torch.empty((T, Q), dtype=proj.dtype, device=dev)
-        check(lib.qs_hyb_latent_prepare(cq.data_ptr(), proj.data_ptr(), proj.stride(0), self.col_q, self.col_kv, self.gain_q.data_ptr(),
+        cq = torch.empty((T, Q), dtype=proj.dtype, device=dev) if Q else None
+        check(lib.qs_hyb_latent_prepare(_p(cq), proj.data_ptr(), proj.stride(0), self.col_q, self.col_kv, _p(self.gain_q),
                                         self.gain_kv.data_ptr(), _p(self.inv_freq), self.rot_dims, _p(b.tok_slot), _p(b.tok_pos), _p(b.block_table),
-                                        b.block_table.shape[1], pool.data_ptr(), T, Q, K, R, page_size, self.eps, dt, stream))
-        q = torch.mm(cq, self.w_uq.t())                                          # [T, H (D + R)]
+                                        b.block_table.shape[1], pool.data_ptr(), T, Q, K, R, page_size, self.eps, self.rot_layout, self.amp, dt, stream))
+        q = torch.mm(cq, self.w_uq.t()) if Q else proj[:, :H * (D + R)]          # [T, H (D + R)]
         fast = scratch is not None and LATENT_IMPL != "plain" and lib.qs_hyb_latent_attention_fast_supported(dt, H, K, R) == 1
         # portions of at least StepBatch.TILE_MIN tokens: per-head keys and values (less arithmetic per score than the K + R numbers of a cell);
         # single tokens and short portions: queries taken to the latent, scored against the cells as they lie
-        per_head = fast and self.per_head_ok and LATENT_IMPL != "latent" and b.n_tiles > 0 and b.n_ctx_pages > 0
+        per_head = scratch is not None and self.per_head_ok and LATENT_IMPL not in ("plain", "latent") and b.n_tiles > 0 and b.n_ctx_pages > 0
         latent = not per_head or b.n_short > 0
         qa = olat = ov = otok = None
         if latent:
-            qlat = torch.bmm(q.view(T, H, D + R)[:, :, :D].transpose(0, 1), self.w_uk)  # [H, T, K]
+            qlat = torch.bmm(q.unflatten(1, (H, D + R))[:, :, :D].transpose(0, 1), self.w_uk)  # [H, T, K]
             qa = torch.empty((T, H, K + R), dtype=proj.dtype, device=dev)
         check(lib.qs_hyb_latent_query(_p(qa), qlat.data_ptr() if latent else None, q.data_ptr(), q.stride(0), _p(self.inv_freq), self.rot_dims,
-                                      _p(b.tok_pos), T, H, D, K, R, 1 if per_head else 0, dt, stream))
+                                      _p(b.tok_pos), T, H, D, K, R, 1 if per_head else 0, self.rot_layout, self.amp, dt, stream))
         if per_head:
             cells = pool.index_select(0, b.ctx_src).view(-1, K + R)
             keys, values = torch.mm(cells, self.w_keys.t()), torch.mm(cells[:, :K], self.w_values.t())
@@ -405,22 +496,23 @@ class LatentAttentionMixer(_Mixer):
             check(lib.qs_hyb_attention_fast(otok.data_ptr(), otok.stride(0), q.data_ptr(), q.stride(0), keys.data_ptr(), values.data_ptr(), _p(b.tok_slot),
                                             _p(b.tok_pos), b.ctx_table.data_ptr(), b.ctx_table.shape[1], _p(b.tile_entry), _p(b.tile_row0), b.n_tiles,
                                             _p(b.long_tokens), b.n_long, None, 0, _p(b.entry_start), _p(b.entry_len), _p(b.entry_slot), _p(b.entry_pos0),
-                                            scratch.data_ptr(), H, H, 1, D + R, Dv, m.scale, 0.0, 1.0, self.eps, 0, page_size, m.chunk, m.window, None, dt,
-                                            stream))
+                                            scratch.data_ptr(), H, H, 1, D + R, Dv, m.scale, 0.0, 1.0, self.eps, 0, page_size, m.chunk, m.window,
+                                            _p(self.sinks), None, dt, stream))
         if latent:
             olat = torch.empty((H, T, K), dtype=proj.dtype, device=dev)
             if fast:
                 check(lib.qs_hyb_latent_attention_fast(olat.data_ptr(), qa.data_ptr(), pool.data_ptr(), _p(b.tok_slot), _p(b.tok_pos), _p(b.block_table),
                                                        b.block_table.shape[1], _p(b.tile_entry), _p(b.tile_row0), 0 if per_head else b.n_tiles,
                                                        _p(b.short_tokens), b.n_short, _p(b.entry_start), _p(b.entry_len), _p(b.entry_slot),
-                                                       _p(b.entry_pos0), T, scratch.data_ptr(), H, K, R, m.scale, page_size, m.chunk, m.window, dt, stream))
+                                                       _p(b.entry_pos0), T, scratch.data_ptr(), H, K, R, m.scale, page_size, m.chunk, m.window,
+                                                       _p(self.sinks), dt, stream))
             else:
                 check(lib.qs_hyb_latent_attention(olat.data_ptr(), qa.data_ptr(), pool.data_ptr(), _p(b.tok_slot), _p(b.tok_pos), _p(b.block_table),
-                                                  b.block_table.shape[1], T, H, K, R, m.scale, page_size, m.chunk, m.window, dt, stream))
+                                                  b.block_table.shape[1], T, H, K, R, m.scale, page_size, m.chunk, m.window, _p(self.sinks), dt, stream))
             ov = torch.bmm(olat, self.w_uv)                                      # [H, T, Dv]
         check(lib.qs_hyb_latent_gate_out(out.data_ptr(), out.stride(0), _p(ov), _p(otok), otok.stride(0) if per_head else 0, _p(b.tok_entry),
                                          _p(b.entry_len), StepBatch.TILE_MIN if latent else 1, proj.data_ptr() if m.gate else None, proj.stride(0),
-                                         self.col_g, T, H, Dv, dt, stream))
+                                         self.col_g, T, H, Dv, 1 if m.gate_wide else 0, dt, stream))
 
 
 LATENT_IMPL = None  # tests: "plain" keeps the latent attention on the CUDA-core kernel, "latent" keeps prompt portions on the latent-space tiles
@@ -468,7 +560,8 @@ class ParallelMixer(_Mixer):
 
 
 MIXERS = {AttentionMixerConfig: MultiMapAttentionMixer, DeltaMixerConfig: GatedDeltaMixer, GateRecurrenceMixerConfig: GateRecurrenceMixer,
-          RetentionMixerConfig: RetentionMixer, ParallelMixerConfig: ParallelMixer, LatentAttentionMixerConfig: LatentAttentionMixer}
+          RetentionMixerConfig: RetentionMixer, ParallelMixerConfig: ParallelMixer, LatentAttentionMixerConfig: LatentAttentionMixer,
+          GatedLinearMixerConfig: GatedLinearMixer}
 
 
 # ------------------------------------------------------------------------------------------------------------------------
@@ -561,18 +654,35 @@ class MoeFeedForward:
 
 
 class DenseFeedForward:
-    """W_down (gelu_tanh(W_gate h) * W_up h)."""
+    """W_down (act(W_gate h + b_gate) * (W_up h + b_up)) [+ b_down], act gelu_tanh or silu.  The down projection's bias (`out_bias`) is left
+    to the block, which adds it where it takes the rows."""
 
     def __init__(self, c: MlpConfig, w: Dict[str, torch.Tensor], width: int, dtype, device):
         st = lambda t: t.to(device=device, dtype=dtype).contiguous()
-        self.ff = c.ff
+        if not c.gated:
+            raise NotImplementedError("a dense feed-forward without a gate, outside a parallel block")
+        if c.act not in _ACT:
+            raise ValueError(f"unknown activation {c.act!r}")
+        if tuple(w["gate"].shape) != (c.ff, width) or tuple(w["up"].shape) != (c.ff, width) or tuple(w["down"].shape) != (width, c.ff):
+            raise ValueError("dense feed-forward: the projections do not match ff x width")
+        self.ff, self.act = c.ff, _ACT[c.act]
         self.w_in, self.w_down = st(torch.cat([w["gate"], w["up"]], 0)), st(w["down"])
+        self.in_bias = self.out_bias = None
+        if c.bias:
+            self.in_bias = torch.cat([w["gate.b"], w["up.b"]], 0).to(torch.float32).to(device).contiguous()
+            self.out_bias = w["down.b"].to(torch.float32).to(device).contiguous()
+            if self.in_bias.numel() != 2 * c.ff or self.out_bias.numel() != width:
+                raise ValueError("dense feed-forward: the biases do not match their projections")
 
     def run(self, h: torch.Tensor, dt: int, stream):
         gu = torch.mm(h, self.w_in.t())
         act = torch.empty((h.shape[0], self.ff), dtype=h.dtype, device=h.device)
-        check(lib.qs_hyb_gelu_tanh_mul(act.data_ptr(), act.stride(0), gu.data_ptr(), h.shape[0], self.ff, dt, stream))
-        return torch.mm(act, self.w_down.t()), False
+        if self.in_bias is None and self.act == 0:
+            check(lib.qs_hyb_gelu_tanh_mul(act.data_ptr(), act.stride(0), gu.data_ptr(), h.shape[0], self.ff, dt, stream))
+        else:
+            check(lib.qs_hyb_bias_gated_act(act.data_ptr(), act.stride(0), gu.data_ptr(), gu.stride(0), _p(self.in_bias), h.shape[0], self.ff, self.act, dt,
+                                            stream))
+        return _mm_f32(act, self.w_down.t()), True
 
 
 FEED_FORWARDS = {MoeConfig: MoeFeedForward, MlpConfig: DenseFeedForward}
@@ -598,6 +708,7 @@ class _Layer:
         self.norm1_b = self.norm2_b = self.mlp_in_bias = self.out_bias = self.side_ff = None
         self.w_all_in = None  # mixer and feed-forward input projections stacked (blocks whose branches read one normed row)
         self.gated = True
+        self.ls1 = self.ls2 = None  # post-norm blocks: per-channel scales of the normed sublayer outputs
 
 
 class HybridDecoder:
@@ -607,7 +718,10 @@ class HybridDecoder:
                   product: [mixer heads | ff activation] @ [W_o | W_down]^T, so the sum of the branches is accumulated in fp32 inside the GEMM.
     "sequential": x <- x + mixer(norm1 x), then x <- x + ff(norm2 x), on `streams` residual streams [T, streams, W] whose read, write and
                   mixing coefficients belong to the sublayer (one stream with coefficients 1 is the plain residual).  A sublayer's write to
-                  the streams happens inside the next sublayer's norm kernel."""
+                  the streams happens inside the next sublayer's norm kernel.
+    "post":       x <- x + ls1 norm1(mixer(x)), then x <- x + ls2 norm2(ff(x)): a sublayer takes the un-normed stream (its storage-type copy is
+                  written by the kernel that lands the previous sublayer), and its fp32 output rows are normed, scaled per channel and
+                  added in one kernel."""
 
     def __init__(self, cfg: HybridConfig, weights: Dict[str, torch.Tensor], dtype: torch.dtype = torch.bfloat16, device: Optional[torch.device] = None):
         if dtype not in _DT:
@@ -631,7 +745,7 @@ class HybridDecoder:
         self.head = st(weights["head"])
         self.final_norm = f32(weights["final.norm"])
         self.layers: List[_Layer] = []
-        if cfg.block not in ("parallel", "sequential"):
+        if cfg.block not in ("parallel", "sequential", "post"):
             raise ValueError(f"unknown block form {cfg.block!r}")
         self.n_streams = max(cfg.streams, 1) if cfg.block == "sequential" else 1
         one = torch.ones(1, dtype=torch.float32, device=dev)
@@ -648,12 +762,29 @@ class HybridDecoder:
             pre = f"l{i}."
             mw = {k[len(pre) + 4:]: v for k, v in weights.items() if k.startswith(pre + "mix.")}
             mixer = MIXERS[type(ly.mixer)](ly.mixer, mw, cfg.eps, dtype, dev)
+            if cfg.block == "post":
+                mixer.place_out(st)
+                ff = norm2 = None
+                if ly.mlp is not None:
+                    fw = {k[len(pre) + 4:]: v for k, v in weights.items() if k.startswith(pre + "mlp.")}
+                    ff, norm2 = FEED_FORWARDS[type(ly.mlp)](ly.mlp, fw, W, dtype, dev), f32(weights[pre + "norm2"])
+                layer = _Layer(mixer, f32(weights[pre + "norm1"]), norm2, None, None, ff)
+                if cfg.layer_scale:
+                    layer.ls1 = f32(weights[pre + "ls1"])
+                    layer.ls2 = f32(weights[pre + "ls2"]) if ff is not None else None
+                for t in (layer.norm1, layer.norm2, layer.ls1, layer.ls2):
+                    if t is not None and t.numel() != W:
+                        raise ValueError(f"{pre}: norm gains and layer scales have `width` numbers")
+                self.layers.append(layer)
+                continue
             if cfg.block == "sequential":
                 mixer.place_out(st)
                 ff, norm2, hc2 = None, None, None
                 if ly.mlp is not None:
                     fw = {k[len(pre) + 4:]: v for k, v in weights.items() if k.startswith(pre + "mlp.")}
                     ff = FEED_FORWARDS[type(ly.mlp)](ly.mlp, fw, W, dtype, dev)
+                    if getattr(ff, "out_bias", None) is not None:
+                        raise NotImplementedError("a biased dense feed-forward on hyper-connected streams")
                     norm2, hc2 = f32(weights[pre + "norm2"]), hyper(pre + "hc2.")
                 self.layers.append(_Layer(mixer, f32(weights[pre + "norm1"]), norm2, None, None, ff, hyper(pre + "hc1."), hc2))
                 continue
@@ -738,6 +869,8 @@ class HybridDecoder:
             scratch = self._scratch
         if cfg.block == "sequential":
             return self._forward_sequential(x, b, cache, tap, scratch, s)
+        if cfg.block == "post":
+            return self._forward_post(x, b, cache, tap, scratch, s)
         return self._forward_parallel(x, b, cache, tap, scratch, s)
 
     def _land(self, x, pending, s, out_h=None, w=None, bias=None, cat_out=None, x0=None) -> None:
@@ -831,6 +964,30 @@ class HybridDecoder:
         self._stream_norm(None, total, x, pending, None, None, s)
         return total
 
+    def _forward_post(self, x, b: StepBatch, cache: HybridCache, tap, scratch, s) -> torch.Tensor:
+        cfg, dev, dt, T, W = self.cfg, self.device, self.dt, b.n_tokens, self.cfg.width
+        # the sublayers' input: the fp32 stream as it is with fp32 storage, else its storage-type copy, which every landing kernel renews
+        if self.dtype == torch.float32:
+            h, h_ptr = x, None
+        else:
+            h = torch.empty((T, W), dtype=self.dtype, device=dev)
+            h_ptr = h.data_ptr()
+            check(lib.qs_hyb_cast_rows(h_ptr, x.data_ptr(), T * W, dt, s))
+        for run, li in enumerate(self.schedule):
+            ly = self.layers[li]
+            proj = torch.mm(h, ly.mixer.w_in.t())
+            cat = torch.empty((T, ly.mixer.out_features), dtype=self.dtype, device=dev)
+            ly.mixer.run(proj, cat, b, cache.runs[run], cache.page_size, scratch, dt, s)
+            y = _mm_f32(cat, ly.mixer.w_out.t())
+            check(lib.qs_hyb_post_norm_update(h_ptr, x.data_ptr(), y.data_ptr(), 1, None, ly.norm1.data_ptr(), _p(ly.ls1), cfg.norm_offset, cfg.eps, T, W, dt, s))
+            if ly.ff is not None:
+                y, y32 = ly.ff.run(h, dt, s)
+                check(lib.qs_hyb_post_norm_update(h_ptr, x.data_ptr(), y.data_ptr(), 1 if y32 else 0, _p(getattr(ly.ff, "out_bias", None)),
+                                                  ly.norm2.data_ptr(), _p(ly.ls2), cfg.norm_offset, cfg.eps, T, W, dt, s))
+            if tap is not None:
+                tap(run, x)
+        return x
+
     def logits(self, x_rows: torch.Tensor) -> torch.Tensor:
         """Final norm and vocabulary projection of the given stream rows -> fp32 [n, vocab]."""
         n, W = x_rows.shape
@@ -846,7 +1003,7 @@ class HybridDecoder:
                                       W, self.dt, s))
         else:
             self._land(x_rows, None, s, out_h=h, w=self.final_norm, bias=self.final_norm_b)
-        out = _mm_f32(h, self.head.t()) if self.cfg.logit_softcap > 0.0 else torch.mm(h, self.head.t()).float()
+        out = _mm_f32(h, self.head.t()) if self.cfg.logit_softcap > 0.0 or self.cfg.block == "post" else torch.mm(h, self.head.t()).float()
         if self.cfg.logit_softcap > 0.0:
             check(lib.qs_hyb_softcap(out.data_ptr(), out.numel(), self.cfg.logit_softcap, s))
         return out
@@ -871,19 +1028,36 @@ def random_weights(cfg: HybridConfig, seed: int = 0, device: Optional[torch.devi
         H, D, Dv = m.heads, m.dim, m.vdim
         if isinstance(m, LatentAttentionMixerConfig):
             K, Q, R = m.kv_rank, m.q_rank, m.rot_dim
-            w[p + "dq"], w[p + "dq.norm"], w[p + "uq"] = r(Q, W, s=W ** -0.5), 1.0 + r(Q, s=0.1), r(H * (D + R), Q, s=Q ** -0.5)
+            if Q:
+                w[p + "dq"], w[p + "dq.norm"], w[p + "uq"] = r(Q, W, s=W ** -0.5), 1.0 + r(Q, s=0.1), r(H * (D + R), Q, s=Q ** -0.5)
+            else:
+                w[p + "q"] = r(H * (D + R), W, s=W ** -0.5)
             w[p + "dkv"], w[p + "dkv.norm"] = r(K + R, W, s=W ** -0.5), 1.0 + r(K, s=0.1)
             w[p + "uk"], w[p + "uv"] = r(H * D, K, s=K ** -0.5), r(H * Dv, K, s=K ** -0.5)
             if m.gate:
-                w[p + "g"] = r(H, W, s=W ** -0.5)
+                w[p + "g"] = r(H * Dv if m.gate_wide else H, W, s=W ** -0.5)
+            if m.sink:
+                w[p + "sink"] = r(H, s=0.5)
+        elif isinstance(m, GatedLinearMixerConfig):
+            rank = m.decay_rank or 16
+            w[p + "q"], w[p + "k"], w[p + "v"], w[p + "g"] = r(H * D, W, s=W ** -0.5), r(H * D, W, s=W ** -0.5), r(H * Dv, W, s=W ** -0.5), r(H * Dv, W, s=W ** -0.5)
+            w[p + "a1"], w[p + "a2"], w[p + "a2.b"], w[p + "norm"] = r(rank, W, s=W ** -0.5), r(H * D, rank, s=rank ** -0.5), 2.0 + r(H * D, s=0.5), 1.0 + r(Dv, s=0.1)
         elif isinstance(m, AttentionMixerConfig):
             G = m.kv_heads
-            w[p + "q"], w[p + "k"], w[p + "v"] = r(H * m.maps * D, W, s=W ** -0.5), r(G * m.maps * D, W, s=W ** -0.5), r(G * Dv, W, s=W ** -0.5)
+            w[p + "q"], w[p + "k"] = r(H * m.maps * D, W, s=W ** -0.5), r(G * m.maps * D, W, s=W ** -0.5)
+            if not m.tied_values:
+                w[p + "v"] = r(G * Dv, W, s=W ** -0.5)
+            if m.qk_gain:
+                w[p + "q.norm"], w[p + "k.norm"] = 1.0 + r(D, s=0.1), 1.0 + r(D, s=0.1)
+            if m.head_gate:
+                w[p + "g"] = r(H, W, s=W ** -0.5)
             if m.maps == 2:
                 for n in ("lq1", "lk1", "lq2", "lk2"):
                     w[p + n] = r(D, s=0.1)
             if m.bias:
-                w[p + "q.b"], w[p + "k.b"], w[p + "v.b"] = r(H * D, s=0.1), r(G * D, s=0.1), r(G * Dv, s=0.1)
+                w[p + "q.b"], w[p + "k.b"] = r(H * D, s=0.1), r(G * D, s=0.1)
+                if not m.tied_values:
+                    w[p + "v.b"] = r(G * Dv, s=0.1)
             if m.head_temp:
                 w[p + "temp"] = 1.0 + r(H, s=0.1)
             if m.sink:
@@ -940,6 +1114,12 @@ def random_weights(cfg: HybridConfig, seed: int = 0, device: Optional[torch.devi
                     w[p + "mlp.gate"] = r(ly.mlp.ff, W, s=W ** -0.5)
                 if ly.mlp.bias:
                     w[p + "mlp.up.b"], w[p + "mlp.down.b"] = r(ly.mlp.ff, s=0.1), r(W, s=0.1)
+                    if ly.mlp.gated:
+                        w[p + "mlp.gate.b"] = r(ly.mlp.ff, s=0.1)
+        if cfg.layer_scale:
+            w[p + "ls1"] = 0.5 + r(W, s=0.05)
+            if ly.mlp is not None:
+                w[p + "ls2"] = 0.5 + r(W, s=0.05)
         if cfg.streams > 0:
             ns = cfg.streams
             for q in (1, 2) if ly.mlp is not None else (1,):

@@ -92,6 +92,17 @@ class AttentionMixerConfig:
     sink: bool = False       # the softmax denominator has one more term exp(sink[h]) without a value
     chunk: int = 0           # > 0: a query sees only keys of its own chunk of this many positions (counted from position 0)
     window: int = 0          # > 0: a query sees at most this many latest positions, its own included
+    keep_first: int = 0      # with a window: the first keep_first positions of the sequence stay visible to every later query
+    qk_gain: bool = False    # unit-RMS q / k are multiplied by learned gains of `dim` numbers shared by the heads (tensors q.norm, k.norm)
+    tied_values: bool = False  # no value projection: a position's value is the key projection's output (bias included), taken ahead of the unit-RMS step
+    distance_slope: float = 0.0  # > 0: slope_h (i - j) is taken off the score of query i and key j, slope_h = 2^(-distance_slope (h + 1) / heads)
+    head_gate: bool = False  # head h's output is multiplied by sigmoid((W_g x)_h) (tensor g [heads, width])
+
+    def slopes(self):
+        """Per-head slope of the distance bias (float64 list), or None."""
+        if self.distance_slope <= 0.0:
+            return None
+        return [2.0 ** (-self.distance_slope * (h + 1) / self.heads) for h in range(self.heads)]
 
 
 @dataclass(frozen=True)
@@ -113,6 +124,18 @@ class RetentionMixerConfig:
     rot: Optional[RotaryConfig]
     decay: Tuple[float, ...]
     gated: bool = True
+
+
+@dataclass(frozen=True)
+class GatedLinearMixerConfig:
+    """Gated linear attention: per head a [dim, vdim] fp32 state, S <- diag(a) S + k v^T with a decay per key channel
+    a = sigmoid(z)^(1/tau), z a low-rank projection (rank `decay_rank`) of the mixer's input plus a bias; o = S^T q with q times dim^-1/2;
+    unit-RMS heads with a gain shared by the heads, times silu of an output gate."""
+    heads: int
+    dim: int
+    vdim: int
+    tau: float
+    decay_rank: int
 
 
 @dataclass(frozen=True)
@@ -139,8 +162,10 @@ class DeltaMixerConfig:
 class LatentAttentionMixerConfig:
     """Causal softmax attention whose keys and values are linear images of a small latent row per position: only that row (`kv_rank` numbers,
     unit RMS times a gain) and one rotated key part of `rot_dim` numbers shared by all heads are cached.  Queries pass a latent of `q_rank`
-    numbers (unit RMS times a gain); a head's query has `dim` unrotated and `rot_dim` rotated numbers, its value `vdim`.  `gate`: every head's
-    output is multiplied by the sigmoid of a projection of the mixer's input (one number per head)."""
+    numbers (unit RMS times a gain; q_rank 0: queries are projected from the mixer's input directly, tensor q); a head's query has `dim`
+    unrotated and `rot_dim` rotated numbers, its value `vdim`.  `gate`: the heads' outputs are multiplied by the sigmoid of a projection of
+    the mixer's input, one number per head, or (`gate_wide`) one per output number.  `sink`: one more term exp(sink[h]) in head h's softmax
+    denominator."""
     heads: int
     dim: int
     rot_dim: int
@@ -152,15 +177,19 @@ class LatentAttentionMixerConfig:
     gate: bool = True
     chunk: int = 0
     window: int = 0
+    gate_wide: bool = False
+    sink: bool = False
 
 
 @dataclass(frozen=True)
 class MlpConfig:
-    """Dense feed-forward.  gated: W_down(gelu_tanh(W_gate h) * W_up h); not gated: W_down gelu_tanh(W_up h).  bias: every projection has one."""
+    """Dense feed-forward.  gated: W_down(act(W_gate h) * W_up h); not gated: W_down act(W_up h).  bias: every projection has one.
+    act: "gelu_tanh" or "silu"."""
     kind: str
     ff: int
     gated: bool = True
     bias: bool = False
+    act: str = "gelu_tanh"
 
 
 @dataclass(frozen=True)
@@ -208,7 +237,8 @@ class HybridConfig:
     pair_mul_prev: int = 0
     pair_mul_cur: int = 0
     norm_offset: float = 1.0  # gains are stored as offsets from this value
-    block: str = "parallel"   # "parallel": x += mixer(norm1 x) + ff(norm2 x);  "sequential": x += mixer(norm1 x), then x += ff(norm2 x)
+    block: str = "parallel"   # "parallel": x += mixer(norm1 x) + ff(norm2 x);  "sequential": x += mixer(norm1 x), then x += ff(norm2 x);
+                              # "post": x += ls1 norm1(mixer(x)), then x += ls2 norm2(ff(x)): the un-normed stream goes into a sublayer, what comes out is normed
     streams: int = 0          # sequential blocks: > 0 = that many residual streams with hyper-connection coefficients (tensors hc1.*, hc2.*)
     norm_groups: int = 1      # RMS norms work on this many equal consecutive parts of the width, each with its own statistic
     embed_scale: float = 1.0
@@ -216,6 +246,7 @@ class HybridConfig:
     shared_norm: bool = False  # parallel blocks: the mixer and the feed-forward read ONE normed row (norm1; there is no norm2)
     loop_in: bool = False     # before the first layer of every pass of the loop: x <- W [x; x0] (tensor loop.in [W, 2 W], x0 the embedding output)
     logit_softcap: float = 0.0  # > 0: logits <- cap * tanh(logits / cap)
+    layer_scale: bool = False   # "post" blocks: a normed sublayer output is multiplied per channel by a learned row (tensors ls1, ls2)
 
     def schedule(self):
         """Layer index of every layer RUN: layers loop_start .. loop_stop-1 run loop_times times in a row (same weights, own cache / state)."""
@@ -337,8 +368,45 @@ def parse_nusuvik(c: dict) -> HybridConfig:
                         norm_kind="layer", shared_norm=True, loop_in=bool(lp), logit_softcap=float(c.get("logit_softcap") or 0.0))
 
 
+def parse_zuzezen(c: dict) -> HybridConfig:
+    """Zuzezen: post-norm blocks (a sublayer takes the un-normed stream; its output is RMS-normed with a gain kept as an offset from one, scaled per
+    channel and added), a scaled embedding; mixers `latent_attention` (queries projected directly, interleaved rotary pairs with YaRN
+    frequencies on the shared rotated part, a sink, a sigmoid gate per output number), `attention` (grouped heads without a value
+    projection, biased q / k with unit RMS and gains, a linear distance bias, a sliding window that keeps the first positions, a sigmoid
+    gate per head) and `gla` (gated linear attention); dense silu-gated feed-forwards with biases."""
+    layers = []
+    for ly in c["layers"]:
+        m = ly["mixer"]
+        if ly["type"] == "latent_attention":
+            rot = _parse_rot(m["rot"]) if m.get("rot") else None
+            mixer = LatentAttentionMixerConfig(int(m["heads"]), int(m["dim"]), int(m["rot_dim"]), int(m["vdim"]), int(m["kv_rank"]), 0, rot,
+                                               float(m["scale"]), gate=True, gate_wide=True, sink=True)
+            if rot is not None and (rot.dims > mixer.rot_dim or rot.dims % 2):
+                raise ValueError("latent attention rotates an even number of at most rot_dim entries")
+        elif ly["type"] == "attention":
+            mk = m.get("mask") or {}
+            window = int(mk.get("size", 0))
+            keep = int(mk.get("keep_first", 0)) if window > 0 else 0   # without a window every earlier position is visible anyway
+            mixer = AttentionMixerConfig(int(m["heads"]), int(m.get("kv_heads", m["heads"])), int(m["dim"]), int(m.get("vdim", m["dim"])), None,
+                                         float(m["scale"]), bias=True, qk_norm=True, window=window, keep_first=keep, qk_gain=True,
+                                         tied_values=True, distance_slope=8.0, head_gate=True)
+            if mixer.vdim != mixer.dim:
+                raise ValueError("attention whose values are its keys needs vdim == dim")
+        elif ly["type"] == "gla":
+            mixer = GatedLinearMixerConfig(int(m["heads"]), int(m["dim"]), int(m["vdim"]), float(m["tau"]), int(m.get("decay_rank", 0)))
+        else:
+            raise ValueError(f"unknown mixer type {ly['type']!r}")
+        mlp = ly.get("mlp")
+        if mlp is not None and mlp.get("kind") != "dense":
+            raise ValueError(f"unknown feed-forward kind {mlp.get('kind')!r}")
+        layers.append(HybridLayerConfig(ly["type"], mixer, MlpConfig("dense", int(mlp["ff"]), gated=True, bias=True, act="silu") if mlp is not None else None))
+    return HybridConfig("Zuzezen", int(c["vocab"]), int(c["width"]), float(c["norm"]["eps"]), tuple(layers), norm_offset=1.0, block="post",
+                        embed_scale=float((c.get("embedding") or {}).get("scale", 1.0)), layer_scale=True)
+
+
 # config.json "architecture" -> parser.  The quantised Llama-family models of MODELS are built by qserve_b200.decode.DecodeRunner.
-ARCHITECTURES: Dict[str, Callable[[dict], HybridConfig]] = {"Rizurax": parse_rizurax, "Toderax": parse_toderax, "Nusuvik": parse_nusuvik}
+ARCHITECTURES: Dict[str, Callable[[dict], HybridConfig]] = {"Rizurax": parse_rizurax, "Toderax": parse_toderax, "Nusuvik": parse_nusuvik,
+                                                                 "Zuzezen": parse_zuzezen}
 
 
 def read_model_config(model_dir: str) -> HybridConfig:

@@ -178,7 +178,7 @@ def test_latent_attention_kernel(dev, dtype, H, K, R):
     qa, pool, slot, pos, table, mb, T, scale, want = _latent_case(dev, dtype, H, K, R, lens, seed=H + K)
     out = torch.zeros(H, T, K, dtype=dtype, device=dev)
     check(lib.qs_hyb_latent_attention(out.data_ptr(), qa.data_ptr(), pool.data_ptr(), slot.data_ptr(), pos.data_ptr(), table.data_ptr(), mb, T, H, K, R,
-                                      scale, 16, 0, 0, 0 if dtype == torch.bfloat16 else 1, _raw()))
+                                      scale, 16, 0, 0, None, 0 if dtype == torch.bfloat16 else 1, _raw()))
     assert _rows_rel(out, want) < (2e-5 if dtype == torch.float32 else 2.0 ** -7)
 
 
@@ -198,7 +198,7 @@ def test_latent_attention_far_key(dev, dtype, key):
         qa, pool, slot, pos, table, mb, T, scale, want = _latent_case(dev, dtype, H, K, R, [(n, nq), (40, 2)], seed=key, needle=(t, 2, key))
         out = torch.zeros(H, T, K, dtype=dtype, device=dev)
         check(lib.qs_hyb_latent_attention(out.data_ptr(), qa.data_ptr(), pool.data_ptr(), slot.data_ptr(), pos.data_ptr(), table.data_ptr(), mb, T, H, K,
-                                          R, scale, 16, 0, 0, 0 if dtype == torch.bfloat16 else 1, _raw()))
+                                          R, scale, 16, 0, 0, None, 0 if dtype == torch.bfloat16 else 1, _raw()))
         cell = pool[int(table[0, key // 16]), key % 16, :K].double().cpu()
         assert float((want[2, t] - cell).abs().max()) < 1e-2  # the case is what it claims: the direct answer is the cell
         assert float((out[2, t].double().cpu() - cell).abs().max()) < (1e-2 if dtype == torch.float32 else 3e-2)
@@ -222,11 +222,11 @@ def test_latent_attention_tensor_core_kernel(dev, H, K, R):
     ptr = lambda t: t.data_ptr()
     check(lib.qs_hyb_latent_attention_fast(ptr(out), ptr(qa), ptr(pool), ptr(b.tok_slot), ptr(b.tok_pos), ptr(table), mb, ptr(b.tile_entry), ptr(b.tile_row0),
                                            b.n_tiles, ptr(b.short_tokens), b.n_short, ptr(b.entry_start), ptr(b.entry_len), ptr(b.entry_slot),
-                                           ptr(b.entry_pos0), T, ptr(scratch), H, K, R, scale, 16, 0, 0, 0, _raw()))
+                                           ptr(b.entry_pos0), T, ptr(scratch), H, K, R, scale, 16, 0, 0, None, 0, _raw()))
     assert torch.equal(b.tok_pos, pos) and torch.equal(b.tok_slot, slot)
     assert _rows_rel(out, want) < 2.0 ** -7
     plain = torch.zeros_like(out)
-    check(lib.qs_hyb_latent_attention(ptr(plain), ptr(qa), ptr(pool), ptr(slot), ptr(pos), ptr(table), mb, T, H, K, R, scale, 16, 0, 0, 0, _raw()))
+    check(lib.qs_hyb_latent_attention(ptr(plain), ptr(qa), ptr(pool), ptr(slot), ptr(pos), ptr(table), mb, T, H, K, R, scale, 16, 0, 0, None, 0, _raw()))
     assert _rows_rel(out, plain) < 2.0 ** -7
 
 
@@ -252,8 +252,8 @@ def test_latent_attention_tensor_core_far_key(dev, key, window):
         ptr = lambda x: x.data_ptr()
         check(lib.qs_hyb_latent_attention_fast(ptr(out), ptr(qa), ptr(pool), ptr(b.tok_slot), ptr(b.tok_pos), ptr(table), mb, ptr(b.tile_entry),
                                                ptr(b.tile_row0), b.n_tiles, ptr(b.short_tokens), b.n_short, ptr(b.entry_start), ptr(b.entry_len),
-                                               ptr(b.entry_slot), ptr(b.entry_pos0), T, ptr(scratch), H, K, R, scale, 16, 0, window, 0, _raw()))
-        check(lib.qs_hyb_latent_attention(ptr(plain), ptr(qa), ptr(pool), ptr(slot), ptr(pos), ptr(table), mb, T, H, K, R, scale, 16, 0, window, 0, _raw()))
+                                               ptr(b.entry_slot), ptr(b.entry_pos0), T, ptr(scratch), H, K, R, scale, 16, 0, window, None, 0, _raw()))
+        check(lib.qs_hyb_latent_attention(ptr(plain), ptr(qa), ptr(pool), ptr(slot), ptr(pos), ptr(table), mb, T, H, K, R, scale, 16, 0, window, None, 0, _raw()))
         cell = pool[int(table[0, key // 16]), key % 16, :K].double().cpu()
         seen = window == 0 or key > qpos - window
         hit = float((out[2, t].double().cpu() - cell).abs().max()) < 3e-2

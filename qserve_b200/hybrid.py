@@ -3,8 +3,9 @@ paged cache, or a recurrent layer over a state slot) beside an optional feed-for
 
 The model is assembled from a `HybridConfig` (qserve_b200.modelcfg): mixers are looked up in `MIXERS` and feed-forwards in `FEED_FORWARDS`
 by config type, so another design reuses them with other constants.  Layers are "parallel" blocks (mixer and feed-forward read the same
-stream and their output projections are one product) or "sequential" blocks (mixer, then feed-forward) on one or several residual streams
-with learned read / write / mixing coefficients.  A forward pass takes a `StepBatch` -- the flat batch a scheduler step has put together (portions of
+stream and their output projections are one product), "sequential" blocks (mixer, then feed-forward) on one or several residual streams
+with learned read / write / mixing coefficients, or "post" blocks (mixer, then feed-forward, each taking the un-normed stream and normed on the
+way back, with a learned scale per channel).  A forward pass takes a `StepBatch` -- the flat batch a scheduler step has put together (portions of
 prompts beside single decoded tokens) -- and the `HybridCache`; there is no other forward path: whole prompts, portions and decoding
 all go through `HybridDecoder.forward`.
 

@@ -56,7 +56,7 @@ STACK = [gla_layer(), latent_layer(), attention_layer(), latent_layer(heads=2, d
 # ------------------------------------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("width,add_f32,bias,scale", [(40, True, True, True), (33, False, False, True), (2048, True, False, False), (1030, False, True, True),
-                                                      (44, True, True, False)])
+                                                      (44, True, True, False), (9000, True, True, True), (1301, True, False, True)])
 def test_post_norm_update_kernel(dev, dtype, width, add_f32, bias, scale):
     from qserve_b200._lib import check, lib
 

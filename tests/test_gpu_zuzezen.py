@@ -167,6 +167,7 @@ LAYERS = [
     latent_layer(heads=8, dim=16, rot_dim=8, vdim=16, kv_rank=32, mlp=None), latent_layer(heads=5, dim=20, rot_dim=12, vdim=4, kv_rank=9, base=1e6, mlp=None),
     latent_layer(heads=2, dim=2, rot_dim=30, vdim=40, kv_rank=64, scaling=False, mlp=None),
     latent_layer(heads=4, dim=16, rot_dim=16, vdim=16, kv_rank=16, scale=0.5, mlp=None),   # equal sizes everywhere
+    latent_layer(heads=3, dim=8, rot_dim=12, vdim=10, kv_rank=20, rot_dims=6, mlp=None),    # only half of the shared part is turned
     attention_layer(mlp=None), attention_layer(heads=1, kv_heads=1, dim=4, size=1, keep_first=0, mlp=None),
     attention_layer(heads=6, kv_heads=2, dim=10, size=40, keep_first=40, mlp=None), attention_layer(heads=3, kv_heads=3, dim=32, size=7, keep_first=1, mlp=None),
     attention_layer(heads=8, kv_heads=1, dim=16, size=0, keep_first=0, mlp=None),          # no window at all

@@ -12,11 +12,11 @@ def gla_layer(heads=3, dim=12, vdim=20, tau=8.0, rank=5, mlp=None):
     return {"type": "gla", "mixer": {"heads": heads, "dim": dim, "vdim": vdim, "tau": tau}, "mlp": mlp, "_rank": rank}
 
 
-def latent_layer(heads=3, dim=12, rot_dim=8, vdim=20, kv_rank=24, base=300.0, scaling=True, scale=None, mlp="default"):
+def latent_layer(heads=3, dim=12, rot_dim=8, vdim=20, kv_rank=24, base=300.0, scaling=True, scale=None, mlp="default", rot_dims=None):
     m = {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": vdim, "kv_rank": kv_rank,
          "scale": scale if scale is not None else 1.0 / math.sqrt(dim + rot_dim)}
     if rot_dim:
-        m["rot"] = {"dims": rot_dim, "base": base}
+        m["rot"] = {"dims": rot_dim if rot_dims is None else rot_dims, "base": base}   # rot_dims < rot_dim: the rest of the shared part is not turned
         if scaling:
             m["rot"]["scaling"] = {"factor": 4.0, "original": 48, "fast": 16.0, "slow": 2.0}
     return {"type": "latent_attention", "mixer": m, "mlp": dense() if mlp == "default" else mlp}
